@@ -93,11 +93,12 @@ class CacheManager:
         self.device = torch.device(device)
         pages = ceil_div(capacity_tokens, page_size)
         by_need: dict[Any, list[int]] = {}
-        for entry in sorted(needs):
+        # (an entry is a number, or (number, name) for a mixer that keeps several things)
+        for entry in sorted(needs, key=lambda e: e if isinstance(e, tuple) else (e, "")):
             by_need.setdefault(needs[entry], []).append(entry)
         self.paged: list[PagedGroup] = []
         self.states: list[StateGroup] = []
-        self._where: dict[int, tuple[str, int, int]] = {}
+        self._where: dict[Any, tuple[str, int, int]] = {}
         for need, entries in by_need.items():
             if isinstance(need, PagedKeyValues):
                 storage = None

@@ -1,8 +1,10 @@
 from .base import ConfigError
+from .galarax import GalaraxConfig
 from .lfm2 import Lfm2Config
-from .registry import (Architecture, architecture_names, get_architecture, read_config,
+from .registry import (Architecture, architecture_key, architecture_names, get_architecture, read_config,
                        register_architecture, unregister_architecture)
 
-__all__ = ["ConfigError", "Lfm2Config", "Architecture", "architecture_names",
+__all__ = ["ConfigError", "GalaraxConfig", "Lfm2Config", "Architecture", "architecture_key",
+           "architecture_names",
            "get_architecture", "read_config", "register_architecture",
            "unregister_architecture"]

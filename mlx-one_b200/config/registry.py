@@ -1,4 +1,5 @@
-"""One registry from an architecture's name (config.json ``model_type``) to its model.
+"""One registry from an architecture's name (config.json ``model_type``, or ``architecture``
+where a design's config.json calls it so) to its model.
 
 An entry names the typed configuration class and a ``describe`` function that turns a
 configuration into a ``ModelSpec``: plain data that lists, layer by layer, which parts
@@ -28,6 +29,7 @@ class Architecture:
 
 _BUILTIN = {
     "lfm2": "mlx_one_b200.architectures.lfm2:ARCHITECTURE",
+    "galarax": "mlx_one_b200.architectures.galarax:ARCHITECTURE",
 }
 _REGISTERED: dict[str, Architecture] = {}
 
@@ -44,6 +46,19 @@ def unregister_architecture(name: str) -> None:
 
 def architecture_names() -> tuple[str, ...]:
     return tuple(sorted(set(_BUILTIN) | set(_REGISTERED)))
+
+
+def architecture_key(data) -> str | None:
+    """The registry name that a config.json's contents ask for: ``model_type``, else
+    ``architecture`` (a string, or the first of a list), lower-cased unless registered as is."""
+    name = data.get("model_type", data.get("architecture"))
+    if isinstance(name, (list, tuple)):
+        name = name[0] if name else None
+    if not isinstance(name, str):
+        return None
+    if name in _REGISTERED or name in _BUILTIN:
+        return name
+    return name.lower()
 
 
 def get_architecture(name: str) -> Architecture:
@@ -63,7 +78,8 @@ def read_config(model_dir: str | Path) -> tuple[Architecture, Any]:
     if not path.is_file():
         raise ConfigError(f"{path} does not exist")
     data = json.loads(path.read_text())
-    if "model_type" not in data:
+    name = architecture_key(data)
+    if name is None:
         raise ConfigError(f"{path} has no model_type")
-    entry = get_architecture(data["model_type"])
+    entry = get_architecture(name)
     return entry, entry.config_class.from_dict(data)

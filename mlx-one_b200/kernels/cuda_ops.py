@@ -55,6 +55,8 @@ class CudaOps:
         except OSError as exc:
             raise KernelBuildError(f"cannot load the CUDA extension: {exc}") from exc
         self.lib.mlxone_last_error.restype = ctypes.c_char_p
+        self.lib.mlxone_gated_delta_scratch.restype = ctypes.c_longlong
+        self.lib.mlxone_gated_delta_state.restype = ctypes.c_longlong
         if self.lib.mlxone_abi_version() != 1:
             raise KernelBuildError("the CUDA extension is of another version; rebuild it")
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -387,6 +389,104 @@ class CudaOps:
             return None
         return self.linear(a, w, bias)
 
+    # ---- activations of a feed-forward without a gate
+
+    ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+    def activation(self, x, kind):
+        """relu2 (max(z, 0)^2), gelu_tanh, silu or relu of every value."""
+        if kind not in self.ACTIVATIONS:
+            raise KernelError(f"unknown activation {kind!r}")
+        self._need(x, x.dtype, "x")
+        out = torch.empty_like(x)
+        self._call("mlxone_activation", _c_void_p(_ptr(x)), _c_void_p(_ptr(out)),
+                   _c_ll(x.numel()), _c_int(self.ACTIVATIONS[kind]), _c_int(_dtype_code(x.dtype)))
+        return out
+
+    def linear_act(self, a, w, kind):
+        """act(a @ w^T): the product followed by the activation kernel."""
+        return self.activation(self.linear(a, w), kind)
+
+    # ---- the 32-bit stream
+
+    def add_vectors(self, residual, delta, token_ids, table, vector):
+        """In place: residual[t] += delta[t] (if given) + table[token_ids[t]] (if a table is
+        given) + vector (if given; float32 [hidden])."""
+        self._need(residual, torch.float32, "residual")
+        tokens, hidden = residual.shape
+        code = _F32
+        for tensor, what in ((delta, "delta"), (table, "table")):
+            if tensor is not None:
+                self._need(tensor, tensor.dtype, what)
+                code = _dtype_code(tensor.dtype)
+        if delta is not None and table is not None and delta.dtype != table.dtype:
+            raise KernelError("delta and table differ in dtype")
+        if delta is not None and delta.shape != residual.shape:
+            raise KernelError("delta and residual differ in shape")
+        if table is not None and table.shape[1] != hidden:
+            raise KernelError("table rows and residual rows differ in length")
+        if vector is not None:
+            self._need(vector, torch.float32, "vector")
+            if vector.numel() != hidden:
+                raise KernelError("vector and residual rows differ in length")
+        self._call("mlxone_add_vectors", _c_void_p(_ptr(residual)), _c_void_p(_ptr(delta)),
+                   _c_void_p(_ptr(token_ids)), _c_void_p(_ptr(table)), _c_void_p(_ptr(vector)),
+                   _c_int(tokens), _c_int(hidden),
+                   _c_int(0 if table is None else table.shape[0]), _c_int(code))
+
+    def normed_mean_add(self, residual, outputs, weights, eps):
+        """In place: residual += mean over branches of x / rms(x) * weight (rms over the row,
+        eps inside the root), all in 32-bit."""
+        self._need(residual, torch.float32, "residual")
+        count = len(outputs)
+        if not 1 <= count <= 4 or len(weights) != count:
+            raise KernelError("one to four branches, each with a weight")
+        for x, weight in zip(outputs, weights):
+            self._need(x, outputs[0].dtype, "branch output")
+            self._need(weight, torch.float32, "branch weight")
+            if x.shape != residual.shape or weight.numel() != residual.shape[1]:
+                raise KernelError("branch outputs and weights must match the residual")
+        xs = (ctypes.c_void_p * count)(*[x.data_ptr() for x in outputs])
+        ws = (ctypes.c_void_p * count)(*[w.data_ptr() for w in weights])
+        self._call("mlxone_normed_mean_add", _c_void_p(_ptr(residual)), xs, ws, _c_int(count),
+                   _c_int(residual.shape[0]), _c_int(residual.shape[1]), _c_float(eps),
+                   _c_int(_dtype_code(outputs[0].dtype)))
+
+    # ---- the gated delta rule
+
+    def gated_delta_rule(self, projected, *, conv, a_log, dt_bias, norm_weight, eps, unit_eps, ctx,
+                         view, write, heads, kv_heads, key_dim, value_dim, taps):
+        """From the fused projection [tokens, q | k | v | gate | beta | decay] to the mixer's
+        gated output [tokens, heads * value_dim]: convolutions with silu, unit-length queries
+        and keys, the recurrence over each request's tokens on its 32-bit state, the output's
+        norm and gate. The state slot holds the heads' matrices and the convolutions' inputs."""
+        tokens = projected.shape[0]
+        self._need(projected, projected.dtype, "projected")
+        qk, inner = kv_heads * key_dim, heads * value_dim
+        if projected.shape[1] != 2 * qk + 2 * inner + 2 * heads:
+            raise KernelError("the projection's width does not match the head counts")
+        for tensor, what in ((conv, "conv"), (a_log, "A_log"), (dt_bias, "dt_bias"),
+                             (norm_weight, "norm weight"), (view.state, "state")):
+            self._need(tensor, torch.float32, what)
+        size = self.lib.mlxone_gated_delta_state(heads, kv_heads, key_dim, value_dim, taps)
+        if view.state[0].numel() != size:
+            raise KernelError(f"a state slot has {view.state[0].numel()} values, the mixer needs {size}")
+        scratch = torch.empty(self.lib.mlxone_gated_delta_scratch(tokens, heads, kv_heads, key_dim,
+                                                                  value_dim),
+                              dtype=torch.float32, device=self.device)
+        out = torch.empty((tokens, inner), dtype=projected.dtype, device=self.device)
+        self._call("mlxone_gated_delta", _c_void_p(_ptr(projected)), _c_void_p(_ptr(conv)),
+                   _c_void_p(_ptr(a_log)), _c_void_p(_ptr(dt_bias)), _c_void_p(_ptr(norm_weight)),
+                   _c_float(eps), _c_float(unit_eps), _c_void_p(_ptr(view.state)),
+                   _c_void_p(_ptr(view.slots)), _c_void_p(_ptr(ctx.token_request)),
+                   _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(ctx.history)),
+                   _c_void_p(_ptr(scratch)), _c_void_p(_ptr(out)), _c_int(tokens),
+                   _c_int(ctx.requests), _c_int(heads), _c_int(kv_heads), _c_int(key_dim),
+                   _c_int(value_dim), _c_int(taps), _c_int(1 if write else 0),
+                   _c_int(_dtype_code(projected.dtype)))
+        self.launches += 2
+        return out
+
     def swiglu(self, gate_up):
         rows, twice = gate_up.shape
         out = torch.empty((rows, twice // 2), dtype=gate_up.dtype, device=self.device)
@@ -454,12 +554,39 @@ class CudaOps:
                                ctx=ctx, view=view, write=write)
 
     def qk_norm_rope_store(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps,
-                           rotary, ctx, view, write):
+                           rotary, ctx, view, write, value_dim=None, amplitude=1.0,
+                           norm_after=False):
+        """Queries [tokens, heads, row] ready for attention; keys and values written to the
+        pages. ``value_dim``, ``amplitude`` (a factor on cosine and sine) and ``norm_after``
+        (queries and keys divided by their root mean square after the rotation, no weight)
+        select the general kernel, which pads queries, keys and values with zeros to the
+        pages' row size."""
         tokens = qkv.shape[0]
         self._need(qkv, view.kv.dtype, "qkv")
+        inv_freq, rotary_dim = (None, 0) if rotary is None else rotary
+        row_dim = view.kv.shape[-1]
+        value_dim = value_dim or head_dim
+        if value_dim != head_dim or row_dim != head_dim or amplitude != 1.0 or norm_after:
+            if qkv.shape[1] != (heads + kv_heads) * head_dim + kv_heads * value_dim:
+                raise KernelError("qkv width does not match the head counts")
+            if norm_after and eps is None:
+                raise KernelError("a norm after the rotation needs its eps")
+            mode = 2 if norm_after else (1 if q_weight is not None else 0)
+            q = torch.empty((tokens, heads, row_dim), dtype=qkv.dtype, device=self.device)
+            self._call("mlxone_qk_prep_general", _c_void_p(_ptr(qkv)), _c_void_p(_ptr(q_weight)),
+                       _c_void_p(_ptr(k_weight)), _c_float(0.0 if eps is None else eps),
+                       _c_void_p(_ptr(inv_freq)), _c_int(rotary_dim), _c_float(amplitude),
+                       _c_int(mode), _c_void_p(_ptr(ctx.positions)),
+                       _c_void_p(_ptr(ctx.token_request)), _c_void_p(_ptr(q)),
+                       _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                       _c_int(view.block_table.shape[1]), _c_int(view.page_size),
+                       _c_int(view.kv.shape[1]), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
+                       _c_int(head_dim), _c_int(value_dim), _c_int(row_dim),
+                       _c_int(1 if write else 0), _c_int(_dtype_code(qkv.dtype)),
+                       _c_void_p(_ptr(self.error_flag)))
+            return q
         if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
             raise KernelError("qkv width does not match the head counts")
-        inv_freq, rotary_dim = (None, 0) if rotary is None else rotary
         q = torch.empty((tokens, heads, head_dim), dtype=qkv.dtype, device=self.device)
         pages = view.kv.shape[1]
         self._call("mlxone_qk_prep", _c_void_p(_ptr(qkv)), _c_void_p(_ptr(q_weight)),
@@ -474,7 +601,7 @@ class CudaOps:
         return q
 
     def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
-                      scale, window, ctx, view, write):
+                      scale, window, ctx, view, write, **extra):
         """From the fused projection qkv [tokens, (heads + 2 kv_heads) * head_dim] to the mixed
         heads [tokens, heads * head_dim]: per-head norm of queries and keys, rotation, keys and
         values appended to the pages, attention. A step of single tokens in bfloat16 whose head
@@ -482,6 +609,16 @@ class CudaOps:
         one kernel; everything else as the preparation kernel followed by attention."""
         tokens = qkv.shape[0]
         inv_freq, rotary_dim = (None, 0) if rotary is None else rotary
+        if extra:
+            # (value size, amplitude, norm after the rotation: see qk_norm_rope_store) the
+            # general preparation, then attention over rows of the pages' size; the output has
+            # that row size per head, zeros behind the values
+            q = self.qk_norm_rope_store(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                        q_weight=q_weight, k_weight=k_weight, eps=eps,
+                                        rotary=rotary, ctx=ctx, view=view, write=write, **extra)
+            return self.paged_attention(q, heads=heads, kv_heads=kv_heads,
+                                        head_dim=view.kv.shape[-1], scale=scale, window=window,
+                                        ctx=ctx, view=view)
         if (self.fused_decode_attention and qkv.dtype == torch.bfloat16
                 and ctx.max_portion == 1 and tokens == ctx.requests
                 and self.tensor_core_attention

@@ -3,10 +3,10 @@ from .base import (Block, FeedForward, FixedState, Mixer, Norm, NormedInput, Pag
                    Part, PositionEncoding, Runtime, StateView, StepContext)
 from .model import Model, cache_entries, expected_tensors
 from .registry import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS
-from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec, TensorSpec
+from .spec import Injection, LayerCall, LayerSpec, ModelSpec, PartSpec, TensorSpec
 
 __all__ = ["Block", "FeedForward", "FixedState", "Mixer", "Norm", "NormedInput", "PagedKeyValues",
            "PagedView", "Part", "PositionEncoding", "Runtime", "StateView", "StepContext",
            "Model", "cache_entries", "expected_tensors", "BLOCKS", "FEED_FORWARDS", "MIXERS",
-           "NORMS", "POSITIONS", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
+           "NORMS", "POSITIONS", "Injection", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
            "TensorSpec"]

@@ -219,6 +219,10 @@ class PositionEncoding(Part):
         rotate queries and keys by position * frequency; None for no rotation."""
         return None
 
+    def amplitude(self) -> float:
+        """A factor on both the cosine and the sine of every angle (1: a pure rotation)."""
+        return 1.0
+
 
 class Block(Part):
     """Arranges a layer's parts. Gets the built parts by role."""

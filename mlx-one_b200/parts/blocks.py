@@ -11,6 +11,7 @@ class PreNormBlock(Block):
     """h = x + mixer(norm(x)); out = h + feed_forward(norm(h)). Each residual add is fused
     with the norm that follows it, so the block returns its last output unadded; a part that
     ``fuses_residual`` may instead add its output into the stream itself and return None.
+    A layer without a feed-forward ends after the mixer.
     Reference: src/mlx_one/models/language/lfm2/reference_math.py:160-179."""
 
     @staticmethod
@@ -25,6 +26,8 @@ class PreNormBlock(Block):
             mixed = self.mixer.forward(normed, ctx, cache, write, residual=residual)
         else:
             mixed = self.mixer.forward(normed, ctx, cache, write)
+        if self.feed_forward is None:
+            return mixed
         normed = self._norm(self.feed_forward_norm, residual, mixed, self.feed_forward)
         if self.feed_forward.fuses_residual:
             return self.feed_forward.forward(normed, ctx, residual=residual)

@@ -1,50 +1,78 @@
-"""Sequence mixers: grouped-query attention over paged keys and values, and the gated
-short convolution with a fixed-size state."""
+"""Sequence mixers: grouped-query attention over paged keys and values, the gated short
+convolution with a fixed-size state, the gated delta rule with a matrix state per head, and
+several mixers side by side on one input."""
 
 from __future__ import annotations
 
 import torch
 
 from .base import FixedState, Mixer, PagedKeyValues
-from .registry import MIXERS, POSITIONS
+from .registry import MIXERS, NORMS, POSITIONS
 from .spec import PartSpec, TensorSpec
 
 
 @MIXERS.register("attention")
 class Attention(Mixer):
     """Grouped-query attention. Parameters: ``hidden``, ``heads``, ``kv_heads``,
-    ``head_dim``, ``qk_norm_eps`` (None = no per-head RMSNorm of queries and keys),
-    ``position`` (a position-encoding PartSpec), ``window`` (None = all keys),
-    ``scale`` (None = head_dim^-0.5).
+    ``head_dim`` (size of a query and key head), ``value_dim`` (size of a value head; None =
+    head_dim), ``bias`` (the three input projections have biases), ``qk_norm_eps`` (None = no
+    per-head RMSNorm of queries and keys), ``qk_norm`` (``weighted_before``: with a stored
+    weight, before the rotation; ``plain_after``: without a weight, after the rotation),
+    ``position`` (a position-encoding PartSpec), ``window`` (None = all keys), ``scale`` (None =
+    head_dim^-0.5).
 
     q, k, v projections (one fused matrix product), per-head RMSNorm of q and k, rotation,
     keys and values appended to the request's pages, causal softmax(q k^T scale) v where
-    query head h reads key head h // (heads / kv_heads), output projection.
+    query head h reads key head h // (heads / kv_heads), output projection. Keys and values
+    share pages whose rows have max(head_dim, value_dim) entries: the shorter of the two is
+    padded with zeros (as are the queries), and the output matrix gets zero columns for the
+    padding of the values, so the attention kernels see one head size.
     Reference: src/mlx_one/models/language/lfm2/reference_math.py:52-111; window mask
     src/mlx_one/models/shared/hybrid.py:14-20."""
 
+    @staticmethod
+    def _sizes(spec):
+        head_dim = spec["head_dim"]
+        value_dim = spec.get("value_dim") or head_dim
+        return head_dim, value_dim, max(head_dim, value_dim)
+
+    @staticmethod
+    def _norm_kind(spec):
+        if spec.get("qk_norm_eps") is None:
+            return None
+        kind = spec.get("qk_norm") or "weighted_before"
+        if kind not in ("weighted_before", "plain_after"):
+            raise ValueError(f"unknown qk_norm {kind!r}")
+        return kind
+
     @classmethod
     def tensors(cls, spec):
-        hidden, hd = spec["hidden"], spec["head_dim"]
-        q_dim, kv_dim = spec["heads"] * hd, spec["kv_heads"] * hd
+        hidden = spec["hidden"]
+        hd, vd, _ = cls._sizes(spec)
+        q_dim, k_dim, v_dim = spec["heads"] * hd, spec["kv_heads"] * hd, spec["kv_heads"] * vd
         out = {
             "q_proj.weight": TensorSpec((q_dim, hidden)),
-            "k_proj.weight": TensorSpec((kv_dim, hidden)),
-            "v_proj.weight": TensorSpec((kv_dim, hidden)),
-            "out_proj.weight": TensorSpec((hidden, q_dim)),
+            "k_proj.weight": TensorSpec((k_dim, hidden)),
+            "v_proj.weight": TensorSpec((v_dim, hidden)),
+            "out_proj.weight": TensorSpec((hidden, spec["heads"] * vd)),
         }
-        if spec.get("qk_norm_eps") is not None:
+        if spec.get("bias"):
+            out["q_proj.bias"] = TensorSpec((q_dim,), "bias")
+            out["k_proj.bias"] = TensorSpec((k_dim,), "bias")
+            out["v_proj.bias"] = TensorSpec((v_dim,), "bias")
+        if cls._norm_kind(spec) == "weighted_before":
             out["q_layernorm.weight"] = TensorSpec((hd,), "norm")
             out["k_layernorm.weight"] = TensorSpec((hd,), "norm")
         return out
 
     @classmethod
     def cache_need(cls, spec):
-        return PagedKeyValues(spec["kv_heads"], spec["head_dim"], spec.get("window"))
+        return PagedKeyValues(spec["kv_heads"], cls._sizes(spec)[2], spec.get("window"))
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
-        self.heads, self.kv_heads, self.head_dim = spec["heads"], spec["kv_heads"], spec["head_dim"]
+        self.heads, self.kv_heads = spec["heads"], spec["kv_heads"]
+        self.head_dim, self.value_dim, self.row_dim = self._sizes(spec)
         if self.heads % self.kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
         self.window = spec.get("window")
@@ -52,26 +80,47 @@ class Attention(Mixer):
         self.scale = float(self.head_dim ** -0.5 if scale is None else scale)
         self.qkv = self.matrix(torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
                                           tensors["v_proj.weight"]], dim=0))
-        self.out = self.matrix(tensors["out_proj.weight"])
+        self.qkv_bias = None
+        if spec.get("bias"):
+            self.qkv_bias = self.vector(torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"],
+                                                   tensors["v_proj.bias"]], dim=0))
+        out = tensors["out_proj.weight"]
+        if self.value_dim < self.row_dim:
+            # zero columns where the values' rows are padded
+            wide = out.new_zeros((out.shape[0], self.heads, self.row_dim))
+            wide[:, :, :self.value_dim] = out.view(out.shape[0], self.heads, self.value_dim)
+            out = wide.view(out.shape[0], self.heads * self.row_dim)
+        self.out = self.matrix(out)
+        self.norm_kind = self._norm_kind(spec)
         self.eps = spec.get("qk_norm_eps")
         self.q_norm = self.k_norm = None
-        if self.eps is not None:
+        if self.norm_kind == "weighted_before":
             self.q_norm = self.vector(tensors["q_layernorm.weight"])
             self.k_norm = self.vector(tensors["k_layernorm.weight"])
         position: PartSpec = spec.get("position") or PartSpec("none")
         self.position = POSITIONS.get(position.kind)(position, {}, runtime)
-        self.ops.check_attention_sizes(self.heads, self.kv_heads, self.head_dim)
+        self.ops.check_attention_sizes(self.heads, self.kv_heads, self.row_dim)
+        # what the plain form of the operation (one head size, weighted norm before a pure
+        # rotation) does not cover goes to the kernels as extra arguments
+        self.extra = {}
+        if (self.value_dim != self.head_dim or self.norm_kind == "plain_after"
+                or self.position.amplitude() != 1.0):
+            self.extra = dict(value_dim=self.value_dim, amplitude=self.position.amplitude(),
+                              norm_after=self.norm_kind == "plain_after")
 
     fuses_residual = True
     accepts_normed_input = True
 
+    def inner_parts(self):
+        return (self.position,)
+
     def forward(self, x, ctx, cache, write, residual=None):
-        qkv = self.ops.linear(x, self.qkv)
+        qkv = self.ops.linear(x, self.qkv, self.qkv_bias)
         mixed = self.ops.qkv_attention(
             qkv, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm, k_weight=self.k_norm, eps=self.eps,
             rotary=self.position.rotary_table(), scale=self.scale, window=self.window, ctx=ctx,
-            view=cache, write=write)
+            view=cache, write=write, **self.extra)
         if residual is None:
             return self.ops.linear(mixed, self.out)
         return self.ops.linear_add(mixed, self.out, None, residual)
@@ -126,3 +175,138 @@ class ShortConv(Mixer):
         if residual is None:
             return self.ops.linear(gated, self.out_proj, self.out_bias)
         return self.ops.linear_add(gated, self.out_proj, self.out_bias, residual)
+
+
+@MIXERS.register("gated_delta")
+class GatedDeltaRule(Mixer):
+    """A linear-attention mixer whose state is one matrix S [key_dim, value_dim] per value head,
+    kept in 32-bit from token to token. Parameters: ``hidden``, ``heads`` (value heads),
+    ``kv_heads`` (query/key heads; value head h reads query/key head h // (heads / kv_heads)),
+    ``key_dim``, ``value_dim``, ``taps``, ``eps`` (of the output norm).
+
+    q, k = W x [kv_heads * key_dim], v = W x [heads * value_dim]; each channel passes a causal
+    convolution over the last ``taps`` tokens of its request (``conv`` [channels, taps], last
+    column the current token's) and silu. Per head q and k become unit vectors,
+    x / sqrt(sum x^2 + 1e-6), and q is scaled by key_dim^-0.5. beta = sigmoid(W_b x) and the decay
+    g = exp(-exp(A_log) softplus(W_a x + dt_bias)) are one number per value head. Then, per
+    token and head: S = g S; u = beta (v - S^T k); S = S + k u^T; o = S^T q. The output is
+    o / rms(o) (over value_dim, with ``eps``) * norm * silu(W_g x), projected by W_o.
+    Everything after the convolutions' silu is 32-bit. The state of a request is S of every
+    head and the last taps - 1 inputs of every convolution, in one 32-bit slot."""
+
+    UNIT_EPS = 1e-6
+
+    @classmethod
+    def _channels(cls, spec):
+        qk = spec["kv_heads"] * spec["key_dim"]
+        return qk, spec["heads"] * spec["value_dim"]
+
+    @classmethod
+    def tensors(cls, spec):
+        hidden, heads, taps = spec["hidden"], spec["heads"], spec["taps"]
+        qk, inner = cls._channels(spec)
+        return {
+            "q": TensorSpec((qk, hidden)), "q.conv": TensorSpec((qk, taps), "wide"),
+            "k": TensorSpec((qk, hidden)), "k.conv": TensorSpec((qk, taps), "wide"),
+            "v": TensorSpec((inner, hidden)), "v.conv": TensorSpec((inner, taps), "wide"),
+            "b": TensorSpec((heads, hidden)), "a": TensorSpec((heads, hidden)),
+            "A_log": TensorSpec((heads,), "wide"), "dt_bias": TensorSpec((heads,), "wide"),
+            "norm": TensorSpec((spec["value_dim"],), "norm"),
+            "g": TensorSpec((inner, hidden)), "o": TensorSpec((hidden, inner)),
+        }
+
+    @classmethod
+    def state_size(cls, spec):
+        qk, inner = cls._channels(spec)
+        matrices = spec["heads"] * spec["key_dim"] * spec["value_dim"]
+        return matrices + (spec["taps"] - 1) * (2 * qk + inner)
+
+    @classmethod
+    def cache_need(cls, spec):
+        return FixedState((cls.state_size(spec),), "float32")
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.sizes = dict(heads=spec["heads"], kv_heads=spec["kv_heads"], key_dim=spec["key_dim"],
+                          value_dim=spec["value_dim"], taps=spec["taps"])
+        if spec["heads"] % spec["kv_heads"]:
+            raise ValueError("heads must be a multiple of kv_heads")
+        # one product for everything that reads x: q | k | v | gate | beta | decay
+        self.project = self.matrix(torch.cat([tensors[name] for name in
+                                              ("q", "k", "v", "g", "b", "a")], dim=0))
+        self.conv = self.vector(torch.cat([tensors[name] for name in
+                                           ("q.conv", "k.conv", "v.conv")], dim=0))
+        self.a_log = self.vector(tensors["A_log"])
+        self.dt_bias = self.vector(tensors["dt_bias"])
+        self.norm = self.vector(tensors["norm"])
+        self.out = self.matrix(tensors["o"])
+        self.eps = float(spec["eps"])
+
+    fuses_residual = True
+    accepts_normed_input = True
+
+    def forward(self, x, ctx, cache, write, residual=None):
+        projected = self.ops.linear(x, self.project)
+        mixed = self.ops.gated_delta_rule(
+            projected, conv=self.conv, a_log=self.a_log, dt_bias=self.dt_bias,
+            norm_weight=self.norm, eps=self.eps, unit_eps=self.UNIT_EPS, ctx=ctx, view=cache,
+            write=write, **self.sizes)
+        if residual is None:
+            return self.ops.linear(mixed, self.out)
+        return self.ops.linear_add(mixed, self.out, None, residual)
+
+
+@MIXERS.register("parallel")
+class ParallelMixers(Mixer):
+    """Several mixers side by side on the same input. Parameters: ``hidden``, ``eps``,
+    ``branches``: a tuple of (name, mixer PartSpec, stored name of the branch's output weight).
+    Every branch's output is divided by its root mean square over the model width (with
+    ``eps``) and multiplied by its weight [hidden]; the mixer's output is the mean of these,
+    added to the 32-bit stream without being rounded first. Each branch keeps what its mixer
+    needs (pages, a state slot) under its name."""
+
+    @classmethod
+    def _branches(cls, spec):
+        return [(name, part, MIXERS.get(part.kind), weight)
+                for name, part, weight in spec["branches"]]
+
+    @classmethod
+    def tensors(cls, spec):
+        out = {}
+        for name, part, kind, weight in cls._branches(spec):
+            for local, want in kind.tensors(part).items():
+                out[part.stored_name(local)] = want
+            out[weight] = TensorSpec((spec["hidden"],), "norm")
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        needs = {name: kind.cache_need(part) for name, part, kind, _ in cls._branches(spec)}
+        return {name: need for name, need in needs.items() if need is not None} or None
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.eps = float(spec["eps"])
+        self.names, self.branches, self.weights = [], [], []
+        for name, part, kind, weight in self._branches(spec):
+            local = {key: tensors[part.stored_name(key)] for key in kind.tensors(part)}
+            self.names.append(name)
+            self.branches.append(kind(part, local, runtime))
+            self.weights.append(self.vector(tensors[weight]))
+
+    fuses_residual = True
+
+    def inner_parts(self):
+        parts = list(self.branches)
+        for branch in self.branches:
+            parts += list(getattr(branch, "inner_parts", lambda: ())())
+        return parts
+
+    def forward(self, x, ctx, cache, write, residual=None):
+        cache = cache or {}
+        outputs = [branch.forward(x, ctx, cache.get(name), write)
+                   for name, branch in zip(self.names, self.branches)]
+        if residual is None:
+            raise ValueError("side-by-side mixers add their mean into the stream themselves")
+        self.ops.normed_mean_add(residual, outputs, self.weights, self.eps)
+        return None

@@ -23,36 +23,63 @@ def expected_tensors(spec: ModelSpec) -> dict[str, TensorSpec]:
         for registry, part in ((BLOCKS, layer.block), (MIXERS, layer.mixer),
                                (NORMS, layer.mixer_norm), (FEED_FORWARDS, layer.feed_forward),
                                (NORMS, layer.feed_forward_norm)):
-            out.update(_part_tensors(registry, part, layer.prefix))
+            if part is not None:
+                out.update(_part_tensors(registry, part, layer.prefix))
     out.update(_part_tensors(NORMS, spec.final_norm, ""))
+    out.update(spec.vectors)
     if spec.head is not None:
         out[spec.head] = TensorSpec((spec.vocab_size, spec.hidden_size))
     return out
 
 
-def cache_entries(spec: ModelSpec) -> dict[int, Any]:
-    """Cache entry -> need, for every entry that a call of the order writes."""
-    needs: dict[int, Any] = {}
+def entry_key(entry: int, name: str | None = None):
+    """The key of a cache entry: the entry's number, or (number, name) for one of the several
+    things that a mixer made of several mixers keeps."""
+    return entry if name is None else (entry, name)
+
+
+def _needs_of(spec: ModelSpec, call: LayerCall, index: int) -> dict[Any, Any]:
+    entry = index if call.cache is None else call.cache
+    layer = spec.layers[call.layer]
+    need = MIXERS.get(layer.mixer.kind).cache_need(layer.mixer)
+    if need is None:
+        return {}
+    if isinstance(need, Mapping):
+        return {entry_key(entry, name): part for name, part in need.items() if part is not None}
+    return {entry: need}
+
+
+def cache_entries(spec: ModelSpec) -> dict[Any, Any]:
+    """Cache entry -> need, for every entry that a call of the order writes. A mixer whose
+    ``cache_need`` is a mapping name -> need (several mixers side by side) has one entry per
+    name, keyed (entry, name)."""
+    needs: dict[Any, Any] = {}
     for index, call in enumerate(spec.order):
-        entry = index if call.cache is None else call.cache
-        layer = spec.layers[call.layer]
-        need = MIXERS.get(layer.mixer.kind).cache_need(layer.mixer)
-        if need is None:
+        if not call.writes_cache:
             continue
-        if call.writes_cache:
-            if entry in needs and needs[entry] != need:
-                raise ValueError(f"cache entry {entry} is written with two different needs")
-            needs[entry] = need
+        for key, need in _needs_of(spec, call, index).items():
+            if key in needs and needs[key] != need:
+                raise ValueError(f"cache entry {key} is written with two different needs")
+            needs[key] = need
     for index, call in enumerate(spec.order):
-        entry = index if call.cache is None else call.cache
-        layer = spec.layers[call.layer]
-        need = MIXERS.get(layer.mixer.kind).cache_need(layer.mixer)
-        if need is not None and not call.writes_cache:
-            if entry not in needs:
-                raise ValueError(f"call {index} reads cache entry {entry} that nothing writes")
-            if needs[entry] != need:
-                raise ValueError(f"call {index} reads cache entry {entry} of another shape")
+        if call.writes_cache:
+            continue
+        for key, need in _needs_of(spec, call, index).items():
+            if key not in needs:
+                raise ValueError(f"call {index} reads cache entry {key} that nothing writes")
+            if needs[key] != need:
+                raise ValueError(f"call {index} reads cache entry {key} of another shape")
     return needs
+
+
+def view_of(views: Mapping[Any, Any], entry: int):
+    """What a call's mixer gets as ``cache``: the entry's view, or for a mixer of several
+    mixers a dict name -> view."""
+    if entry in views:
+        return views[entry]
+    named = {key[1]: view for key, view in views.items()
+             if isinstance(key, tuple) and key[0] == entry}
+    return named or None
 
 
 class Model:
@@ -80,25 +107,34 @@ class Model:
             roles = dict(
                 mixer=build(MIXERS, layer.mixer, layer.prefix),
                 mixer_norm=build(NORMS, layer.mixer_norm, layer.prefix),
-                feed_forward=build(FEED_FORWARDS, layer.feed_forward, layer.prefix),
-                feed_forward_norm=build(NORMS, layer.feed_forward_norm, layer.prefix),
+                feed_forward=None if layer.feed_forward is None
+                else build(FEED_FORWARDS, layer.feed_forward, layer.prefix),
+                feed_forward_norm=None if layer.feed_forward_norm is None
+                else build(NORMS, layer.feed_forward_norm, layer.prefix),
             )
             self.layers.append(build(BLOCKS, layer.block, layer.prefix, **roles))
         self.final_norm = build(NORMS, spec.final_norm, "")
         self.head = (self.embedding if spec.head is None
                      else tensors[spec.head].to(runtime.dtype).contiguous())
         self.order = tuple(
-            LayerCall(call.layer, index if call.cache is None else call.cache, call.writes_cache)
+            LayerCall(call.layer, index if call.cache is None else call.cache, call.writes_cache,
+                      call.inject)
             for index, call in enumerate(spec.order))
+        # what is added to the stream before a call: one 32-bit row per injection
+        self.injected = {}
+        for index, call in enumerate(spec.order):
+            if call.inject is not None and call.inject.vector is not None:
+                rows = tensors[call.inject.vector]
+                if not 0 <= call.inject.row < rows.shape[0]:
+                    raise ValueError(f"{call.inject.vector} has no row {call.inject.row}")
+                self.injected[index] = rows[call.inject.row].to(torch.float32).contiguous()
         self.cache_needs = cache_entries(spec)
         # whether steps of this model may be captured as CUDA graphs: every part says so
         parts = [self.final_norm]
         for block in self.layers:
-            parts += [block, block.mixer, block.mixer_norm, block.feed_forward,
-                      block.feed_forward_norm]
-            position = getattr(block.mixer, "position", None)
-            if position is not None:
-                parts.append(position)
+            parts += [part for part in (block, block.mixer, block.mixer_norm, block.feed_forward,
+                                        block.feed_forward_norm) if part is not None]
+            parts += list(getattr(block.mixer, "inner_parts", lambda: ())())
         self.capturable = all(getattr(part, "capturable", True) for part in parts)
         # For debugging: called as observer(place, residual, delta) after the embedding
         # (place -1) and after every call of a layer (place = its number in the order); the
@@ -112,8 +148,16 @@ class Model:
         if self.observer is not None:
             self.observer(-1, residual, delta)
         for place, call in enumerate(self.order):
+            if call.inject is not None:
+                # the pending output, the token's embedding once more and the pass's vector
+                # enter the 32-bit stream in one kernel
+                self.ops.add_vectors(residual, delta, ctx.token_ids,
+                                     self.embedding if call.inject.embedding else None,
+                                     self.injected.get(place))
+                delta = None
             delta = self.layers[call.layer].forward(residual, delta, ctx,
-                                                    ctx.views.get(call.cache), call.writes_cache)
+                                                    view_of(ctx.views, call.cache),
+                                                    call.writes_cache)
             if self.observer is not None:
                 self.observer(place, residual, delta)
         return residual, delta
@@ -145,6 +189,14 @@ class Model:
                         total += value.numel() * value.element_size()
                 elif hasattr(value, "spec") and hasattr(value, "runtime"):
                     visit(value)
+                elif isinstance(value, (list, tuple)):
+                    for item in value:
+                        if isinstance(item, torch.Tensor):
+                            if item.data_ptr() not in seen:
+                                seen.add(item.data_ptr())
+                                total += item.numel() * item.element_size()
+                        elif hasattr(item, "spec") and hasattr(item, "runtime"):
+                            visit(item)
         for layer in self.layers:
             visit(layer)
         visit(self.final_norm)

@@ -10,18 +10,21 @@ from .spec import TensorSpec
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
     """v * rsqrt(mean(v^2) + eps) * weight over the last axis, computed in 32-bit, fused
-    with the residual add that precedes it. Parameters: ``size``, ``eps``.
+    with the residual add that precedes it. Parameters: ``size``, ``eps``, ``offset`` (0; a
+    weight stored around zero has offset 1 and the norm multiplies by offset + weight).
     Reference: nn.RMSNorm at src/mlx_one/models/language/lfm2/reference_math.py:156-157."""
 
     supports_lazy = True
 
     @classmethod
     def tensors(cls, spec):
-        return {"weight": TensorSpec((spec["size"],), "norm")}
+        return {"weight": TensorSpec((spec["size"],), "norm0" if spec.get("offset") else "norm")}
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
         self.weight = self.vector(tensors["weight"])
+        if spec.get("offset"):
+            self.weight = (self.weight + float(spec["offset"])).contiguous()
         self.eps = float(spec["eps"])
 
     def forward(self, residual, delta, lazy=False):

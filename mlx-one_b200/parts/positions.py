@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import PositionEncoding
@@ -27,6 +29,46 @@ class RotaryEncoding(PositionEncoding):
 
     def rotary_table(self):
         return self.inv_freq, self.rotary_dim
+
+
+@POSITIONS.register("yarn")
+class ScaledRotaryEncoding(PositionEncoding):
+    """Rotary encoding of the first ``rotary_dim`` dimensions of a head (pairs j and j +
+    rotary_dim / 2) whose frequencies are stretched for a context ``factor`` times the
+    ``original`` one: f_j = theta^(-2j / rotary_dim); with d(t) = rotary_dim * ln(original /
+    (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1)
+    and r_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1) the frequency of pair j is
+    (f_j / factor) r_j + f_j (1 - r_j): pairs that turn often within the original context keep
+    their frequency, slow ones are interpolated. Cosine and sine are both multiplied by
+    0.1 ln(factor) + 1. Parameters: ``theta``, ``rotary_dim``, and ``factor``, ``original``,
+    ``fast``, ``slow`` (``factor`` None: plain frequencies, amplitude 1). The table is worked out
+    in 64-bit on the host and rounded once."""
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.rotary_dim = dims = int(spec["rotary_dim"])
+        if dims <= 0 or dims % 2:
+            raise ValueError("rotary_dim must be positive and even")
+        theta = float(spec["theta"])
+        index = torch.arange(dims // 2, dtype=torch.float64)
+        freq = theta ** (-2.0 * index / dims)
+        self.scale = 1.0
+        factor = spec.get("factor")
+        if factor is not None:
+            factor, original = float(factor), float(spec["original"])
+            turns = lambda t: dims * math.log(original / (2 * math.pi * t)) / (2 * math.log(theta))
+            lo = max(math.floor(turns(float(spec["fast"]))), 0)
+            hi = min(math.ceil(turns(float(spec["slow"]))), dims - 1)
+            ramp = torch.clamp((index - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            freq = freq / factor * ramp + freq * (1.0 - ramp)
+            self.scale = 0.1 * math.log(factor) + 1.0
+        self.inv_freq = freq.to(torch.float32).to(runtime.device)
+
+    def rotary_table(self):
+        return self.inv_freq, self.rotary_dim
+
+    def amplitude(self):
+        return self.scale
 
 
 @POSITIONS.register("none")

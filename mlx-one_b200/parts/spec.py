@@ -35,7 +35,8 @@ class PartSpec:
 @dataclass(frozen=True)
 class TensorSpec:
     """Shape of a stored tensor and how the random-weights mode fills it:
-    ``normal`` ~ N(0, std), ``norm`` ~ 1 + N(0, 0.1), ``bias`` ~ N(0, std)."""
+    ``normal`` ~ N(0, std), ``norm`` ~ 1 + N(0, 0.1), ``bias`` ~ N(0, std), ``norm0`` ~
+    N(0, 0.1) (a norm weight stored around zero), ``wide`` ~ N(0, 0.5)."""
 
     shape: tuple[int, ...]
     init: str = "normal"
@@ -43,14 +44,26 @@ class TensorSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: a block arrangement and the parts it arranges, by role."""
+    """One layer: a block arrangement and the parts it arranges, by role. A layer without a
+    feed-forward has ``feed_forward`` and ``feed_forward_norm`` None."""
 
     prefix: str
     block: PartSpec
     mixer: PartSpec
     mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward: PartSpec | None
+    feed_forward_norm: PartSpec | None
+
+
+@dataclass(frozen=True)
+class Injection:
+    """Something added to every token's residual stream right before a call of the order:
+    row ``row`` of the stored tensor ``vector`` ([rows, hidden], listed in
+    ``ModelSpec.vectors``), and, with ``embedding``, the token's embedding once more."""
+
+    vector: str | None = None
+    row: int = 0
+    embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -58,11 +71,13 @@ class LayerCall:
     """One entry of the execution order. ``layer`` indexes ``ModelSpec.layers`` and may
     appear more than once. ``cache`` names the cache entry that the call's mixer uses;
     by default every call has an entry of its own (its index in the order). A call with
-    ``writes_cache=False`` reads an entry that an earlier call of the step has written."""
+    ``writes_cache=False`` reads an entry that an earlier call of the step has written.
+    ``inject`` is added to the stream before the call (a loop's pass that starts here)."""
 
     layer: int
     cache: int | None = None
     writes_cache: bool = True
+    inject: Injection | None = None
 
 
 @dataclass(frozen=True)
@@ -81,3 +96,5 @@ class ModelSpec:
     init_std: float = 0.02
     # (stored name, shape) -> (name, squeeze axis or None), or None to drop the tensor
     rename: Callable[[str, tuple[int, ...]], tuple[str, int | None] | None] | None = None
+    # stored tensors that belong to no part (what ``Injection.vector`` names): name -> TensorSpec
+    vectors: Mapping[str, Any] = field(default_factory=dict)

@@ -2,7 +2,9 @@
 
 Every tensor is drawn in 32-bit on the host from a generator seeded by (seed, tensor
 name), so the same folder comes out on every machine and for every order of tensors:
-matrices, tables, convolution kernels and biases ~ N(0, std); norm weights ~ 1 + N(0, 0.1).
+matrices, tables, convolution kernels and biases ~ N(0, std); norm weights ~ 1 + N(0, 0.1)
+(``norm0``, a weight stored around zero: N(0, 0.1); ``wide``, small per-channel kernels and
+per-head constants that should differ visibly: N(0, 0.5)).
 """
 
 from __future__ import annotations
@@ -14,7 +16,7 @@ from typing import Any, Mapping
 
 import torch
 
-from ..config.registry import get_architecture
+from ..config.registry import architecture_key, get_architecture
 from ..parts.model import expected_tensors
 from .safetensors_io import write_safetensors
 
@@ -42,6 +44,10 @@ def random_tensors(spec, seed: int, dtype: torch.dtype = torch.bfloat16, device=
                              device=device)
         if want.init == "norm":
             values = 1.0 + 0.1 * values
+        elif want.init == "norm0":
+            values = 0.1 * values
+        elif want.init == "wide":
+            values = 0.5 * values
         else:
             values = spec.init_std * values
         out[name] = values.to(dtype)
@@ -54,7 +60,7 @@ def write_random_model(folder: str | Path, config: Mapping[str, Any], seed: int,
     config.json keys, ``model_type`` included) and returns the folder."""
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    entry = get_architecture(config["model_type"])
+    entry = get_architecture(architecture_key(config) or "")
     typed = entry.config_class.from_dict(config)
     spec = entry.describe(typed)
     write_safetensors(folder / "model.safetensors", random_tensors(spec, seed, dtype),

@@ -99,16 +99,22 @@ class PlainOps:
                                ctx=ctx, view=view, write=write)
 
     def qk_norm_rope_store(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps,
-                           rotary, ctx, view, write):
+                           rotary, ctx, view, write, value_dim=None, amplitude=1.0,
+                           norm_after=False):
         tokens = qkv.shape[0]
         dtype = qkv.dtype
-        split = qkv.float().view(tokens, heads + 2 * kv_heads, head_dim)
-        q, k, v = split[:, :heads], split[:, heads:heads + kv_heads], split[:, heads + kv_heads:]
+        value_dim = value_dim or head_dim
+        row_dim = view.kv.shape[-1]
+        flat = qkv.float()
+        q = flat[:, :heads * head_dim].view(tokens, heads, head_dim)
+        k = flat[:, heads * head_dim:(heads + kv_heads) * head_dim].view(tokens, kv_heads, head_dim)
+        v = flat[:, (heads + kv_heads) * head_dim:].view(tokens, kv_heads, value_dim)
 
         def norm(x, weight):
-            if weight is None:
+            if weight is None and not norm_after:
                 return x
-            return x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps) * weight
+            x = x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps)
+            return x if weight is None else x * weight
 
         def rotate(x):
             if rotary is None:
@@ -116,12 +122,17 @@ class PlainOps:
             inv_freq, rotary_dim = rotary
             half = rotary_dim // 2
             angles = ctx.positions.float()[:, None] * inv_freq[None, :]
-            cos, sin = torch.cos(angles)[:, None, :], torch.sin(angles)[:, None, :]
+            cos = (torch.cos(angles) * amplitude)[:, None, :]
+            sin = (torch.sin(angles) * amplitude)[:, None, :]
             a, b = x[..., :half], x[..., half:rotary_dim]
             return torch.cat((a * cos - b * sin, b * cos + a * sin, x[..., rotary_dim:]), dim=-1)
 
-        q = rotate(norm(q, q_weight)).to(dtype)
-        k = rotate(norm(k, k_weight)).to(dtype)
+        pad = lambda x: torch.nn.functional.pad(x, (0, row_dim - x.shape[-1]))
+        if norm_after:
+            q, k = norm(rotate(q), None), norm(rotate(k), None)
+        else:
+            q, k = rotate(norm(q, q_weight)), rotate(norm(k, k_weight))
+        q, k, v = pad(q).to(dtype), pad(k).to(dtype), pad(v).to(dtype)
         if write:
             positions = ctx.positions.tolist()
             requests = ctx.token_request.tolist()
@@ -131,16 +142,95 @@ class PlainOps:
                 assert page >= 0, "a key is written to a position without a page"
                 offset = positions[t] % view.page_size
                 view.kv[0, page, :, offset] = k[t]
-                view.kv[1, page, :, offset] = v[t].to(dtype)
+                view.kv[1, page, :, offset] = v[t]
         return q.contiguous()
 
     def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
-                      scale, window, ctx, view, write):
+                      scale, window, ctx, view, write, **extra):
         q = self.qk_norm_rope_store(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
                                     q_weight=q_weight, k_weight=k_weight, eps=eps, rotary=rotary,
-                                    ctx=ctx, view=view, write=write)
-        return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                    ctx=ctx, view=view, write=write, **extra)
+        return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=view.kv.shape[-1],
                                     scale=scale, window=window, ctx=ctx, view=view)
+
+    def add_vectors(self, residual, delta, token_ids, table, vector):
+        if delta is not None:
+            residual += delta.float()
+        if table is not None:
+            residual += table[token_ids.long()].float()
+        if vector is not None:
+            residual += vector
+
+    def activation(self, x, kind):
+        z = x.float()
+        if kind == "relu2":
+            out = torch.relu(z) ** 2
+        elif kind == "relu":
+            out = torch.relu(z)
+        elif kind == "silu":
+            out = z / (1 + torch.exp(-z))
+        elif kind == "gelu_tanh":
+            out = 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+        else:
+            raise ValueError(kind)
+        return out.to(x.dtype)
+
+    def linear_act(self, a, w, kind):
+        return self.activation(self.linear(a, w), kind)
+
+    def normed_mean_add(self, residual, outputs, weights, eps):
+        total = torch.zeros_like(residual)
+        for out, weight in zip(outputs, weights):
+            x = out.float()
+            total += x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps) * weight
+        residual += total / len(outputs)
+
+    def gated_delta_rule(self, projected, *, conv, a_log, dt_bias, norm_weight, eps, unit_eps, ctx,
+                         view, write, heads, kv_heads, key_dim, value_dim, taps):
+        tokens = projected.shape[0]
+        qk, inner = kv_heads * key_dim, heads * value_dim
+        channels = 2 * qk + inner
+        matrices = heads * key_dim * value_dim
+        flat = projected.float()
+        gate = flat[:, channels:channels + inner].view(tokens, heads, value_dim)
+        beta = torch.sigmoid(flat[:, channels + inner:channels + inner + heads])
+        step = torch.nn.functional.softplus(flat[:, channels + inner + heads:] + dt_bias)
+        decay = torch.exp(-torch.exp(a_log) * step)
+        out = torch.empty(tokens, heads, value_dim)
+        starts, history, slots = ctx.request_start.tolist(), ctx.history.tolist(), view.slots.tolist()
+        silu = lambda z: z / (1 + torch.exp(-z))
+        unit = lambda x: x / torch.sqrt(x.pow(2).sum(dim=-1, keepdim=True) + unit_eps)
+        for r in range(ctx.requests):
+            first, last = starts[r], starts[r + 1]
+            n = last - first
+            slot = view.state[slots[r]]
+            state = slot[:matrices].view(heads, key_dim, value_dim).clone()
+            tail = slot[matrices:].view(max(taps - 1, 0), channels).clone()
+            if taps > 1:
+                valid = torch.arange(taps - 1) + history[r] - (taps - 1) >= 0
+                tail = tail * valid[:, None]
+            padded = torch.cat((tail, flat[first:last, :channels]), dim=0)
+            mixed = sum(padded[j:j + n] * conv[:, j] for j in range(taps))
+            mixed = silu(mixed)
+            q = unit(mixed[:, :qk].view(n, kv_heads, key_dim)) * key_dim ** -0.5
+            k = unit(mixed[:, qk:2 * qk].view(n, kv_heads, key_dim))
+            v = mixed[:, 2 * qk:].view(n, heads, value_dim)
+            for h in range(heads):
+                shared = h // (heads // kv_heads)
+                s = state[h]
+                for t in range(n):
+                    s = decay[first + t, h] * s
+                    u = beta[first + t, h] * (v[t, h] - s.T @ k[t, shared])
+                    s = s + torch.outer(k[t, shared], u)
+                    out[first + t, h] = s.T @ q[t, shared]
+                state[h] = s
+            if write:
+                slot[:matrices] = state.reshape(-1)
+                if taps > 1:
+                    slot[matrices:] = padded[n:n + taps - 1].reshape(-1)
+        out = out * torch.rsqrt(out.pow(2).mean(dim=-1, keepdim=True) + eps) * norm_weight
+        out = out * silu(gate)
+        return out.reshape(tokens, inner).to(projected.dtype)
 
     def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view):
         tokens = q.shape[0]
