@@ -17,6 +17,8 @@ Two more workloads, each printing one JSON line of its own (the default line is 
 
     python bench.py --case batching     continuous batching of 128 requests at the LFM2-700M shape
     python bench.py --case long         4 x 32,768-token prompts at the LFM2-350M shape, then decoding
+    python bench.py --case galarax      Galarax beside LFM2 at equal width, depth and vocabulary:
+                                        decode and prefill throughput, and its new kernels alone
 
 Data: seeded uniform-random token ids and N(0, 0.02) weights (norms 1 + N(0, 0.1)); there
 are no checkpoints offline. Working set per step (2.3 GB of weights) is far larger than L2,
@@ -202,13 +204,16 @@ def model_flops(spec, tokens):
     flops = 0
     for name, tensor in expected_tensors(spec).items():
         if len(tensor.shape) == 2 and name != spec.embedding and name != spec.head \
-                and not name.endswith("conv.conv"):
+                and not name.endswith(("conv.conv", ".conv")) and name not in spec.vectors:
             flops += 2 * tokens * tensor.shape[0] * tensor.shape[1]
     flops += 2 * spec.vocab_size * spec.hidden_size          # one row of logits
-    for layer in spec.layers:
-        if layer.mixer.kind == "attention":
-            width = layer.mixer["heads"] * layer.mixer["head_dim"]
-            flops += 4 * width * tokens * (tokens + 1) // 2   # causal QK^T and PV
+    for call in spec.order:
+        mixer = spec.layers[call.layer].mixer
+        mixers = [part for _, part, _ in mixer["branches"]] if mixer.kind == "parallel" else [mixer]
+        for part in mixers:
+            if part.kind == "attention":
+                width = part["heads"] * part["head_dim"]
+                flops += 4 * width * tokens * (tokens + 1) // 2   # causal QK^T and PV
     return flops
 
 
@@ -626,6 +631,240 @@ def case_long(args) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------- Galarax beside LFM2
+
+
+def galarax_shape(width: int, layers: int, vocab: int = 65536) -> dict:
+    """A Galarax of the sizes that a model of this width has: heads of 64 for the softmax branch
+    (one key head per four query heads, half of a head rotated), heads of 128 x 128 for the delta
+    rule (inner width = model width), a feed-forward four times the width."""
+    left = {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64,
+            "scale": 0.125, "rot": {"base": 1000000.0, "dims": 32, "scaling": {
+                "factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    right = {"heads": width // 128, "kv_heads": width // 256, "dim": 128, "vdim": 128, "conv": 4}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": right},
+             "mlp": {"kind": "dense", "ff": 4 * width}}
+    return {"architecture": "Galarax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [layer] * layers}
+
+
+def engine_of(data, batch, context, steps_ahead, name):
+    """An engine over random weights for any registered architecture's config.json contents."""
+    import torch
+
+    from mlx_one_b200 import BatchingConfig, CacheConfig, Engine
+    from mlx_one_b200.config import architecture_key, get_architecture
+    from mlx_one_b200.engine.loading import LoadedModel, build_model
+    from mlx_one_b200.weights import random_tensors
+
+    architecture = get_architecture(architecture_key(data))
+    typed = architecture.config_class.from_dict(data)
+    spec = architecture.describe(typed)
+    tensors = random_tensors(spec, seed=0, dtype=torch.bfloat16, device="cuda:0")
+    model = build_model(spec, tensors, "bfloat16", "cuda:0")
+    del tensors
+    loaded = LoadedModel(Path(name), architecture, typed, spec, model)
+    capacity = batch * (-(-(context + steps_ahead + 128) // 64) * 64) + PREFILL_TOKENS + 64
+    batching = BatchingConfig(max_sequences=batch, queue_size=batch + 1, prefill_chunk_size=2048,
+                              max_scheduled_tokens=4096, max_prefill_tokens=4096)
+    return Engine(loaded, batching_config=batching,
+                  cache_config=CacheConfig(block_size_tokens=PAGE_SIZE, capacity_tokens=capacity,
+                                           max_requests=batch + 1))
+
+
+def graph_seconds(fn, copies, inner):
+    """Seconds per call of fn(i), i cycling over ``copies`` argument sets, inside a CUDA graph."""
+    import torch
+
+    for i in range(min(copies, 3)):
+        fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(inner):
+            fn(i % copies)
+    graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(5):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / 1e3 / (5 * inner)
+
+
+def galarax_kernels(width, batch, peak):
+    """The kernels that Galarax adds, alone, beside the like kernels of LFM2, for a decode step
+    of ``batch`` tokens and a prompt of PREFILL_TOKENS tokens: algorithmic bytes / time against
+    the measured copy bandwidth. Arguments rotate over copies that together exceed L2."""
+    import torch
+
+    from mlx_one_b200.kernels import default_ops
+    from mlx_one_b200.parts import (FixedState, PagedKeyValues, PagedView, StateView,
+                                    StepContext)
+    from mlx_one_b200.parts.mixers import GatedDeltaRule
+
+    ops, device = default_ops("cuda:0"), "cuda:0"
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=device)
+    bf16 = lambda *shape: torch.randn(*shape, device=device).bfloat16()
+
+    def ctx_of(portions, histories):
+        positions, owner, starts = [], [], [0]
+        for r, (n, before) in enumerate(zip(portions, histories)):
+            positions += list(range(before, before + n))
+            owner += [r] * n
+            starts.append(starts[-1] + n)
+        return StepContext(tokens=len(positions), requests=len(portions),
+                           token_ids=ints([0] * len(positions)), positions=ints(positions),
+                           token_request=ints(owner), request_start=ints(starts),
+                           history=ints(histories), max_portion=max(portions),
+                           max_context=max(p + h for p, h in zip(portions, histories)))
+
+    H, G, D, V, taps = width // 128, width // 256, 128, 128, 4
+    sizes = dict(heads=H, kv_heads=G, key_dim=D, value_dim=V, taps=taps)
+    state_size = GatedDeltaRule.state_size({"heads": H, "kv_heads": G, "key_dim": D,
+                                            "value_dim": V, "taps": taps})
+    channels = 2 * G * D + H * V
+    wide = channels + H * V + 2 * H
+    out = {}
+    for label, portions, histories in (("decode", [1] * batch, [2048] * batch),
+                                       ("prefill", [PREFILL_TOKENS], [0])):
+        ctx = ctx_of(portions, histories)
+        tokens, requests = ctx.tokens, ctx.requests
+        copies = max(2, min(24, int(200e6 // (requests * state_size * 4))))
+        state = torch.zeros(copies * requests, state_size, device=device)
+        views = [StateView(state, ints(list(range(c * requests, (c + 1) * requests))),
+                           FixedState((state_size,), "float32")) for c in range(copies)]
+        projected = [bf16(tokens, wide) for _ in range(copies)]
+        constants = dict(conv=torch.randn(channels, taps, device=device) * 0.5,
+                         a_log=torch.zeros(H, device=device), dt_bias=torch.zeros(H, device=device),
+                         norm_weight=torch.ones(V, device=device), eps=1e-6, unit_eps=1e-6,
+                         ctx=ctx, write=True, **sizes)
+        seconds = graph_seconds(lambda i: ops.gated_delta_rule(projected[i], view=views[i],
+                                                               **constants), copies, 2 * copies)
+        moved = tokens * (wide + H * V) * 2 + 2 * requests * state_size * 4
+        out[f"{label}_gated_delta"] = {
+            "us": round(seconds * 1e6, 2), "gbs": round(moved / seconds / 1e9, 1),
+            "hbm_frac": round(moved / seconds / 1e9 / peak["hbm_gbs"], 4),
+            "gflops": round(6.0 * tokens * H * D * V / seconds / 1e9, 1)}
+        # LFM2's like kernel: the gated short convolution with its slot
+        conv_state = torch.zeros(copies * requests, 2, width, device=device).bfloat16()
+        conv_views = [StateView(conv_state, views[c].slots, FixedState((2, width))) for c in range(copies)]
+        bcx = [bf16(tokens, 3 * width) for _ in range(copies)]
+        kernel = torch.randn(width, 3, device=device)
+        seconds = graph_seconds(lambda i: ops.short_conv(bcx[i], kernel=kernel, bias=None, taps=3,
+                                                         ctx=ctx, view=conv_views[i], write=True),
+                                copies, 2 * copies)
+        moved = tokens * 4 * width * 2 + 2 * requests * 2 * width * 2
+        out[f"{label}_short_conv_lfm2"] = {
+            "us": round(seconds * 1e6, 2), "gbs": round(moved / seconds / 1e9, 1),
+            "hbm_frac": round(moved / seconds / 1e9 / peak["hbm_gbs"], 4)}
+        # preparation of queries and keys with the page write: general form and LFM2's
+        heads, kv_heads, head = width // 64, width // 256, 64
+        pages = -(-(histories[0] + portions[0]) // PAGE_SIZE)
+        table = ints([[r * pages + b for b in range(pages)] for r in range(requests)])
+        kv = torch.zeros(2, requests * pages + 1, kv_heads, PAGE_SIZE, head, device=device).bfloat16()
+        view = PagedView(kv, table, PAGE_SIZE, PagedKeyValues(kv_heads, head, None))
+        qkv = [bf16(tokens, (heads + 2 * kv_heads) * head) for _ in range(copies)]
+        inv_half = torch.rand(16, device=device)
+        inv_full = torch.rand(32, device=device)
+        ones = torch.ones(head, device=device)
+        common = dict(heads=heads, kv_heads=kv_heads, head_dim=head, eps=1e-6, ctx=ctx, view=view,
+                      write=True)
+        moved = tokens * ((heads + 2 * kv_heads) * head * 2) * 2
+        for name, extra in (("qk_prep_general", dict(q_weight=None, k_weight=None, rotary=(inv_half, 32),
+                                                     value_dim=head, amplitude=1.2, norm_after=True)),
+                            ("qk_prep_lfm2", dict(q_weight=ones, k_weight=ones, rotary=(inv_full, 64)))):
+            seconds = graph_seconds(lambda i: ops.qk_norm_rope_store(qkv[i], **common, **extra),
+                                    copies, 2 * copies)
+            out[f"{label}_{name}"] = {"us": round(seconds * 1e6, 2),
+                                      "gbs": round(moved / seconds / 1e9, 1),
+                                      "hbm_frac": round(moved / seconds / 1e9 / peak["hbm_gbs"], 4)}
+        # the mean of two normed branches into the stream, beside add + RMSNorm
+        residual = [torch.zeros(tokens, width, device=device) for _ in range(copies)]
+        a, b = [bf16(tokens, width) for _ in range(copies)], [bf16(tokens, width) for _ in range(copies)]
+        weight = torch.ones(width, device=device)
+        seconds = graph_seconds(lambda i: ops.normed_mean_add(residual[i], [a[i], b[i]],
+                                                              [weight, weight], 1e-6), copies, 2 * copies)
+        moved = tokens * width * (4 + 4 + 2 + 2)
+        out[f"{label}_normed_mean_add"] = {"us": round(seconds * 1e6, 2),
+                                           "hbm_frac": round(moved / seconds / 1e9 / peak["hbm_gbs"], 4)}
+        seconds = graph_seconds(lambda i: ops.add_rmsnorm(residual[i], a[i], weight, 1e-6,
+                                                          torch.bfloat16), copies, 2 * copies)
+        moved = tokens * width * (4 + 4 + 2 + 2)
+        out[f"{label}_add_rmsnorm_lfm2"] = {"us": round(seconds * 1e6, 2),
+                                            "hbm_frac": round(moved / seconds / 1e9 / peak["hbm_gbs"], 4)}
+        # the feed-forward's first product with its activation, beside the gated one of equal output
+        up = [bf16(4 * width, width) * 0.02 for _ in range(copies)]
+        gate_up = [bf16(8 * width, width) * 0.02 for _ in range(copies)]
+        x = bf16(tokens, width)
+        for name, fn, rows_w in (("up_relu2", lambda i: ops.linear_act(x, up[i], "relu2"), 4 * width),
+                                 ("up_swiglu_lfm2", lambda i: ops.linear_swiglu(x, gate_up[i]), 8 * width)):
+            seconds = graph_seconds(fn, copies, copies)
+            entry = {"us": round(seconds * 1e6, 2)}
+            if label == "decode":
+                entry["hbm_frac"] = round(rows_w * width * 2 / seconds / 1e9 / peak["hbm_gbs"], 4)
+            else:
+                entry["tensor_frac"] = round(2.0 * tokens * rows_w * width / seconds / 1e12 /
+                                             peak["bf16_tflops"], 4)
+            out[f"{label}_{name}"] = entry
+        del state, views, projected, conv_state, bcx, kv, qkv, residual, a, b, up, gate_up
+        torch.cuda.empty_cache()
+    return out
+
+
+def case_galarax(args) -> int:
+    """Galarax beside LFM2 at equal width, depth and vocabulary (random weights): decode tokens/s
+    at ``--batch`` and ``--context`` (device-timed graph replays of the engine's step), prefill
+    tokens/s of one 2,048-token prompt, each against its bound, and the new kernels alone."""
+    import gc
+
+    import torch
+
+    peak = peaks()
+    warmup, steps = max(args.warmup, 3), min(args.steps, 128)
+    context = args.context or 2048
+    layers = min(args.layers, 8)
+    results = {}
+    for width, twin in ((1024, LFM2_350M), (2048, LFM2_1_2B)):
+        lfm2 = dict(twin)
+        lfm2["layer_types"] = lfm2["layer_types"][:layers]
+        lfm2["num_hidden_layers"] = layers
+        for label, data in ((f"galarax_w{width}", galarax_shape(width, layers)),
+                            (f"lfm2_w{width}", lfm2)):
+            engine = engine_of(data, args.batch, context, warmup + steps, f"random-{label}")
+            model, spec = engine.model, engine.model.spec
+            weight_bytes = model.weight_bytes()
+            kv_per_token = engine.cache_bytes_per_token()
+            state_bytes = sum(g.storage[:, 0].numel() * g.storage.element_size()
+                              for g in engine.cache.states)
+            seconds, _, mean_context, launches = time_decode(engine, args.batch, context, warmup,
+                                                             steps, seed=3)
+            step_bytes = weight_bytes + args.batch * (mean_context * kv_per_token + 2 * state_bytes)
+            prefill_seconds = time_prefill(engine, PREFILL_TOKENS, 2, 3, seed=5)
+            flops = model_flops(spec, PREFILL_TOKENS)
+            results[label] = {
+                "layers": layers, "weight_mb": round(weight_bytes / 1e6, 1),
+                "state_mb_per_request": round(state_bytes / 1e6, 2),
+                "decode_tokens_per_s": round(args.batch * steps / seconds, 1),
+                "decode_ms_per_step": round(seconds / steps * 1e3, 4),
+                "decode_hbm_frac": round(step_bytes / (seconds / steps) / 1e9 / peak["hbm_gbs"], 4),
+                "launches_per_step": launches,
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_seconds, 1),
+                "prefill_ms": round(prefill_seconds * 1e3, 3),
+                "prefill_tensor_frac": round(flops / prefill_seconds / (peak["bf16_tflops"] * 1e12), 4)}
+            del engine, model
+            gc.collect()
+            torch.cuda.empty_cache()
+        results[f"kernels_w{width}"] = galarax_kernels(width, args.batch, peak)
+    print(json.dumps({"case": "galarax", "batch": args.batch, "context": context, "steps": steps,
+                      "warmup": warmup, "dtype": "bf16", "peaks": peak["source"],
+                      "data": "synthetic: random weights, seeded uniform-random token ids",
+                      "results": results}))
+    return 0
+
+
 def decode_step_case(batch: int, context: int) -> int:
     """A few eager decode steps of the whole model at the benchmark's sizes, for a list of the
     step's launches (`ncu --metrics gpu__time_duration.sum`): the prompts are fed first, the last
@@ -921,7 +1160,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=None,
                         help="context length (default 4096; --case long: prompt tokens, 32768)")
-    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long"],
+    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long", "galarax"],
                         help="decode: the default line; batching: 128 requests batched "
                              "continuously (LFM2-700M shape); long: 4 x 32,768 tokens "
                              "(LFM2-350M shape)")
@@ -949,6 +1188,8 @@ def main() -> int:
         return case_batching(args)
     if args.case == "long":
         return case_long(args)
+    if args.case == "galarax":
+        return case_galarax(args)
     args.context = args.context or 4096
     if args.kernel:
         return kernel_case(args.kernel, args.batch, args.context)

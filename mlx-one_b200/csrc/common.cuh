@@ -55,6 +55,19 @@ __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
 template <typename T>
 __device__ __forceinline__ float round_to(float v) { return to_float<T>(from_float<T>(v)); }
 
+// Activations of a feed-forward without a gate, by the code the C interface uses.
+enum : int { MLXONE_ACT_RELU2 = 0, MLXONE_ACT_GELU_TANH = 1, MLXONE_ACT_SILU = 2, MLXONE_ACT_RELU = 3 };
+
+__device__ __forceinline__ float mlxone_activate(float z, int kind) {
+    switch (kind) {
+        case MLXONE_ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
+        case MLXONE_ACT_GELU_TANH:
+            return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        case MLXONE_ACT_SILU: return z / (1.f + expf(-z));
+        default: return fmaxf(z, 0.f);
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);

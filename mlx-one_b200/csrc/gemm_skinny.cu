@@ -42,7 +42,10 @@ constexpr int SLICE_BYTES = ROWS * SLICE * 2;
 constexpr int WARPS = 16;
 constexpr size_t SHARED_LIMIT = 226 * 1024;      // of the 227 KB that a block may ask for
 
-enum : int { STORE_BF16 = 0, SWIGLU = 1, ADD_RESIDUAL = 2, STORE_F32 = 3, GATED_CONV = 4 };
+enum : int { STORE_BF16 = 0, SWIGLU = 1, ADD_RESIDUAL = 2, STORE_F32 = 3, GATED_CONV = 4,
+             ACTIVATE = 5 };   // ACTIVATE: bf16 store of an activation (its code rides in up_offset)
+// epilogue codes of the C interface from this on mean ACTIVATE with activation (code - this)
+constexpr int ACTIVATE_BASE = 16;
 
 // What the gated-convolution epilogue needs beside the product: one token per request.
 struct ConvUpdate {
@@ -609,6 +612,10 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
             } else if (EPILOGUE == STORE_BF16) {
                 reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
                     __float2bfloat16_rn(value);
+            } else if (EPILOGUE == ACTIVATE) {
+                // (the product is rounded as if it had been stored, then activated)
+                reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] = __float2bfloat16_rn(
+                    mlxone_activate(__bfloat162float(__float2bfloat16_rn(value)), up_offset));
             } else if (EPILOGUE == ADD_RESIDUAL) {
                 // added where the value lives (one addition per address, so the result is the
                 // same): the thread does not wait for the old value to come and go
@@ -712,7 +719,8 @@ cudaError_t launch_for_rows(const void* a, int lda, const void* w, const float* 
 MLXONE_API int mlxone_gemm_skinny_max_rows() { return 32; }
 
 // epilogue: 0 = out bf16 [m, n]; 1 = SwiGLU, w is [gate rows; up rows] with n = 2 * width, out
-// bf16 [m, width]; 2 = out is the float32 residual [m, n], added in place; 3 = out float32.
+// bf16 [m, width]; 2 = out is the float32 residual [m, n], added in place; 3 = out float32;
+// 16 + a = out bf16 [m, n] of activation a (0 relu^2, 1 gelu_tanh, 2 silu, 3 relu).
 MLXONE_API int mlxone_gemm_skinny(const void* a, int lda, const void* w, const float* bias,
                                   void* out, int ldo, int m, int n, int k, int epilogue,
                                   cudaStream_t stream) {
@@ -723,9 +731,15 @@ MLXONE_API int mlxone_gemm_skinny(const void* a, int lda, const void* w, const f
     MLXONE_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(w) & 15) == 0,
                    "gemm_skinny: operands must be 16-byte aligned");
-    MLXONE_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_skinny: unknown epilogue %d", epilogue);
+    MLXONE_REQUIRE((epilogue >= 0 && epilogue <= 3) ||
+                       (epilogue >= ACTIVATE_BASE && epilogue <= ACTIVATE_BASE + MLXONE_ACT_RELU),
+                   "gemm_skinny: unknown epilogue %d", epilogue);
     MLXONE_REQUIRE(epilogue != SWIGLU || n % 2 == 0, "gemm_skinny: SwiGLU needs an even n");
     cudaError_t err;
+    if (epilogue >= ACTIVATE_BASE) {
+        err = launch_for_rows<ACTIVATE>(a, lda, w, bias, out, ldo, m, n, k, epilogue - ACTIVATE_BASE,
+                                        stream);
+    } else
     switch (epilogue) {
         case STORE_BF16:
             err = launch_for_rows<STORE_BF16>(a, lda, w, bias, out, ldo, m, n, k, 0, stream); break;
@@ -839,11 +853,17 @@ MLXONE_API int mlxone_gemm_skinny_norm(const float* source, int source_ld,
                        (reinterpret_cast<uintptr_t>(norm_weight) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(w) & 15) == 0,
                    "gemm_skinny_norm: operands must be 16-byte aligned");
-    MLXONE_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_skinny_norm: unknown epilogue %d", epilogue);
+    MLXONE_REQUIRE((epilogue >= 0 && epilogue <= 3) ||
+                       (epilogue >= ACTIVATE_BASE && epilogue <= ACTIVATE_BASE + MLXONE_ACT_RELU),
+                   "gemm_skinny_norm: unknown epilogue %d", epilogue);
     MLXONE_REQUIRE(epilogue != SWIGLU || n % 2 == 0, "gemm_skinny_norm: SwiGLU needs an even n");
     NormInput norm;
     norm.source = source; norm.ld = source_ld; norm.weight = norm_weight; norm.eps = eps;
     cudaError_t err;
+    if (epilogue >= ACTIVATE_BASE) {
+        err = launch_for_rows<ACTIVATE>(nullptr, 0, w, bias, out, ldo, m, n, k,
+                                        epilogue - ACTIVATE_BASE, stream, norm);
+    } else
     switch (epilogue) {
         case STORE_BF16:
             err = launch_for_rows<STORE_BF16>(nullptr, 0, w, bias, out, ldo, m, n, k, 0, stream, norm); break;

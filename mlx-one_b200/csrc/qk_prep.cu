@@ -207,7 +207,8 @@ qk_prep_wide_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restri
 // The general form: queries and keys of ``head_dim`` values, values of ``value_dim``, all
 // written into rows of ``row_dim`` >= both (zeros behind the shorter ones), so that keys and
 // values share one page geometry. qkv[t] = [heads x head_dim | kv_heads x head_dim | kv_heads x
-// value_dim]. The rotation multiplies cosine and sine by ``amplitude``. norm_mode 0: no norm;
+// value_dim], rows ``ld`` values apart (a slice of a wider product). The rotation multiplies
+// cosine and sine by ``amplitude``. norm_mode 0: no norm;
 // 1: RMSNorm with the given weights before the rotation; 2: division by the root mean square
 // (over head_dim, eps inside the root) after the rotation, no weight. One warp per (token, head).
 template <typename T>
@@ -219,82 +220,95 @@ qk_prep_general_kernel(const T* __restrict__ qkv, const float* __restrict__ q_we
                        const int* __restrict__ token_request, T* __restrict__ q_out,
                        T* __restrict__ kv, const int* __restrict__ block_table, int table_width,
                        int page_size, long long kv_half, int tokens, int heads, int kv_heads,
-                       int head_dim, int value_dim, int row_dim, int write_kv,
+                       int head_dim, int value_dim, int row_dim, int write_kv, int ld,
                        int* __restrict__ error_flag) {
+    // One block per token: the angles' cosines and sines are worked out once for all its heads
+    // (rotary_dim / 2 of each, scaled), then the warps take the token's heads in turn.
     extern __shared__ float shared[];
+    float* cosines = shared;
+    float* sines = shared + rotary_dim / 2;
     griddep_launch();
     griddep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slots_per_token = heads + 2 * kv_heads;
-    const long long item = (long long)blockIdx.x * WARPS + warp;
-    if (item >= (long long)tokens * slots_per_token) return;
-    const int t = (int)(item / slots_per_token);
-    const int slot = (int)(item % slots_per_token);
-    float* values = shared + warp * row_dim;
-    const bool is_q = slot < heads;
-    const bool is_k = !is_q && slot < heads + kv_heads;
-    if (!is_q && !write_kv) return;
-    const size_t width = (size_t)(heads + kv_heads) * head_dim + (size_t)kv_heads * value_dim;
-    const int size = (is_q || is_k) ? head_dim : value_dim;
-    const T* src = qkv + (size_t)t * width +
-                   (is_q || is_k ? (size_t)slot * head_dim
-                                 : (size_t)(heads + kv_heads) * head_dim +
-                                       (size_t)(slot - heads - kv_heads) * value_dim);
-    float sum = 0.f;
-    for (int e = lane; e < row_dim; e += 32) {
-        const float v = e < size ? to_float<T>(src[e]) : 0.f;
-        values[e] = v;
-        sum += v * v;
-    }
+    const int t = blockIdx.x;
     const int position = positions[t];
-    if (is_q || is_k) {
-        const float* weight = is_q ? q_weight : k_weight;
-        if (norm_mode == 1) {
-            sum = warp_sum(sum);
-            const float inv = rsqrtf(sum / (float)head_dim + eps);
-            for (int e = lane; e < head_dim; e += 32)
-                values[e] = values[e] * inv * (weight ? weight[e] : 1.f);
-        }
-        __syncwarp();
-        if (inv_freq != nullptr) {
-            const int half = rotary_dim / 2;
-            for (int j = lane; j < half; j += 32) {
-                const float angle = (float)position * inv_freq[j];
-                float sine, cosine;
-                sincosf(angle, &sine, &cosine);
-                sine *= amplitude;
-                cosine *= amplitude;
-                const float a = values[j], b = values[j + half];
-                values[j] = a * cosine - b * sine;
-                values[j + half] = b * cosine + a * sine;
-            }
-        }
-        __syncwarp();
-        if (norm_mode == 2) {
-            float squares = 0.f;
-            for (int e = lane; e < head_dim; e += 32) squares = fmaf(values[e], values[e], squares);
-            squares = warp_sum(squares);
-            const float inv = 1.f / sqrtf(squares / (float)head_dim + eps);
-            for (int e = lane; e < head_dim; e += 32) values[e] *= inv;
+    const int half = rotary_dim / 2;
+    if (inv_freq != nullptr) {
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            float sine, cosine;
+            sincosf((float)position * inv_freq[j], &sine, &cosine);
+            sines[j] = sine * amplitude;
+            cosines[j] = cosine * amplitude;
         }
     }
-    __syncwarp();
-    T* dst;
-    if (is_q) {
-        dst = q_out + ((size_t)t * heads + slot) * row_dim;
-    } else {
-        const int kv_head = is_k ? slot - heads : slot - heads - kv_heads;
+    __syncthreads();
+    // where this token's keys and values go
+    T* page_base = nullptr;
+    if (write_kv) {
         const int r = token_request[t];
         const int block = position / page_size;
         const int page = block < table_width ? block_table[(size_t)r * table_width + block] : -1;
         if (page < 0) {
-            if (lane == 0) atomicExch(error_flag, 2);
-            return;
+            if (threadIdx.x == 0) atomicExch(error_flag, 2);
+        } else {
+            page_base = kv + ((size_t)page * kv_heads * page_size + position % page_size) * row_dim;
         }
-        dst = kv + (is_k ? 0 : kv_half) +
-              (((size_t)page * kv_heads + kv_head) * page_size + position % page_size) * row_dim;
     }
-    for (int e = lane; e < row_dim; e += 32) dst[e] = from_float<T>(values[e]);
+    float* values = shared + rotary_dim + warp * row_dim;
+    for (int slot = warp; slot < slots_per_token; slot += WARPS) {
+        const bool is_q = slot < heads;
+        const bool is_k = !is_q && slot < heads + kv_heads;
+        if (!is_q && page_base == nullptr) continue;
+        const int size = (is_q || is_k) ? head_dim : value_dim;
+        const T* src = qkv + (size_t)t * ld +
+                       (is_q || is_k ? (size_t)slot * head_dim
+                                     : (size_t)(heads + kv_heads) * head_dim +
+                                           (size_t)(slot - heads - kv_heads) * value_dim);
+        float sum = 0.f;
+        for (int e = lane; e < row_dim; e += 32) {
+            const float v = e < size ? to_float<T>(src[e]) : 0.f;
+            values[e] = v;
+            sum += v * v;
+        }
+        if (is_q || is_k) {
+            const float* weight = is_q ? q_weight : k_weight;
+            if (norm_mode == 1) {
+                sum = warp_sum(sum);
+                const float inv = rsqrtf(sum / (float)head_dim + eps);
+                for (int e = lane; e < head_dim; e += 32)
+                    values[e] = values[e] * inv * (weight ? weight[e] : 1.f);
+            }
+            __syncwarp();
+            float squares = 0.f;
+            if (inv_freq != nullptr) {
+                for (int j = lane; j < half; j += 32) {
+                    const float a = values[j], b = values[j + half];
+                    const float first = a * cosines[j] - b * sines[j];
+                    const float second = b * cosines[j] + a * sines[j];
+                    values[j] = first;
+                    values[j + half] = second;
+                }
+            }
+            __syncwarp();
+            if (norm_mode == 2) {
+                for (int e = lane; e < head_dim; e += 32) squares = fmaf(values[e], values[e], squares);
+                squares = warp_sum(squares);
+                const float inv = 1.f / sqrtf(squares / (float)head_dim + eps);
+                for (int e = lane; e < head_dim; e += 32) values[e] *= inv;
+            }
+        }
+        __syncwarp();
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)t * heads + slot) * row_dim;
+        } else {
+            const int kv_head = is_k ? slot - heads : slot - heads - kv_heads;
+            dst = page_base + (is_k ? 0 : kv_half) + (size_t)kv_head * page_size * row_dim;
+        }
+        for (int e = lane; e < row_dim; e += 32) dst[e] = from_float<T>(values[e]);
+        __syncwarp();
+    }
 }
 
 template <int HD>
@@ -365,7 +379,7 @@ MLXONE_API int mlxone_qk_prep_general(const void* qkv, const float* q_weight, co
                                       const int* token_request, void* q_out, void* kv,
                                       const int* block_table, int table_width, int page_size,
                                       int pages, int tokens, int heads, int kv_heads, int head_dim,
-                                      int value_dim, int row_dim, int write_kv, int dtype,
+                                      int value_dim, int row_dim, int write_kv, int ld, int dtype,
                                       int* error_flag, cudaStream_t stream) {
     if (tokens == 0) return 0;
     MLXONE_REQUIRE(tokens > 0 && heads > 0 && kv_heads > 0, "qk_prep: bad sizes");
@@ -378,10 +392,11 @@ MLXONE_API int mlxone_qk_prep_general(const void* qkv, const float* q_weight, co
                    "qk_prep: rotary size %d must be even and at most the head size %d", rotary_dim,
                    head_dim);
     MLXONE_REQUIRE(norm_mode >= 0 && norm_mode <= 2, "qk_prep: unknown norm mode %d", norm_mode);
+    MLXONE_REQUIRE(ld >= (heads + kv_heads) * head_dim + kv_heads * value_dim,
+                   "qk_prep: rows %d apart are shorter than their heads", ld);
     MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0, "qk_prep: bad page geometry");
-    const long long items = (long long)tokens * (heads + 2 * kv_heads);
-    const int blocks = ceil_div_host(items, WARPS);
-    const size_t shared = (size_t)WARPS * row_dim * sizeof(float);
+    const int blocks = tokens;
+    const size_t shared = (size_t)(rotary_dim + WARPS * row_dim) * sizeof(float);
     const long long kv_half = (long long)pages * kv_heads * page_size * row_dim;
     if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
@@ -389,14 +404,14 @@ MLXONE_API int mlxone_qk_prep_general(const void* qkv, const float* q_weight, co
                       (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, amplitude,
                       norm_mode, positions, token_request, (T*)q_out, (T*)kv, block_table,
                       table_width, page_size, kv_half, tokens, heads, kv_heads, head_dim, value_dim,
-                      row_dim, write_kv, error_flag);
+                      row_dim, write_kv, ld, error_flag);
     } else {
         using T = float;
         launch_kernel(qk_prep_general_kernel<T>, dim3(blocks), dim3(WARPS * 32), shared, stream, true,
                       (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, amplitude,
                       norm_mode, positions, token_request, (T*)q_out, (T*)kv, block_table,
                       table_width, page_size, kv_half, tokens, heads, kv_heads, head_dim, value_dim,
-                      row_dim, write_kv, error_flag);
+                      row_dim, write_kv, ld, error_flag);
     }
     MLXONE_LAUNCH_CHECK("qk_prep_general");
     return 0;

@@ -47,17 +47,8 @@ MLXONE_API int mlxone_add_vectors(float* residual, const void* delta, const int*
 }
 
 // ------------------------------------------------------------------ activations
-enum : int { ACT_RELU2 = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_RELU = 3 };
-
-__device__ __forceinline__ float activate(float z, int kind) {
-    switch (kind) {
-        case ACT_RELU2: { const float r = fmaxf(z, 0.f); return r * r; }
-        case ACT_GELU_TANH:
-            return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-        case ACT_SILU: return z / (1.f + expf(-z));
-        default: return fmaxf(z, 0.f);
-    }
-}
+// (mlxone_activate in common.cuh: relu2, gelu_tanh, silu, relu)
+__device__ __forceinline__ float activate(float z, int kind) { return mlxone_activate(z, kind); }
 
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, long long total,
@@ -150,6 +141,106 @@ __global__ void normed_mean_add_kernel(float* __restrict__ residual, Branches<T>
     }
 }
 
+// Rows of a multiple of 8 values, 16-byte aligned, up to 8192: a thread keeps its 8 (or 16)
+// values of every branch in registers between the sums of squares and the output, so every row
+// is read once, 16 bytes a load, and the branches' sums share one reduction over the block.
+template <typename T>
+__device__ __forceinline__ void load8(const T* src, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* src, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(src)[0], b = reinterpret_cast<const float4*>(src)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* src, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = __low2float(p[i]); v[2 * i + 1] = __high2float(p[i]); }
+}
+
+template <typename T, int COUNT, int ITER>
+__global__ void __launch_bounds__(512)
+normed_mean_add_rows_kernel(float* __restrict__ residual, Branches<T> branches, int hidden,
+                            float eps) {
+    __shared__ float partial[COUNT][16];
+    __shared__ float inverse[COUNT];
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    float x[COUNT][ITER][8];
+    float sum[COUNT];
+#pragma unroll
+    for (int b = 0; b < COUNT; ++b) {
+        sum[b] = 0.f;
+#pragma unroll
+        for (int i = 0; i < ITER; ++i) {
+            const int c = (threadIdx.x + i * blockDim.x) * 8;
+            if (c < hidden) {
+                load8<T>(branches.x[b] + (size_t)t * hidden + c, x[b][i]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sum[b] = fmaf(x[b][i][e], x[b][i][e], sum[b]);
+            }
+        }
+        sum[b] = warp_sum(sum[b]);
+        if (lane == 0) partial[b][warp] = sum[b];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int b = 0; b < COUNT; ++b) {
+            float v = lane < warps ? partial[b][lane] : 0.f;
+            v = warp_sum(v);
+            if (lane == 0) inverse[b] = rsqrtf(v / (float)hidden + eps);
+        }
+    }
+    __syncthreads();
+    const float share = 1.f / (float)COUNT;
+#pragma unroll
+    for (int i = 0; i < ITER; ++i) {
+        const int c = (threadIdx.x + i * blockDim.x) * 8;
+        if (c >= hidden) continue;
+        float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int b = 0; b < COUNT; ++b) {
+            float w[8];
+            load8<float>(branches.weight[b] + c, w);
+            const float inv = inverse[b];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) total[e] += x[b][i][e] * inv * w[e];
+        }
+        float4* dst = reinterpret_cast<float4*>(residual + (size_t)t * hidden + c);
+        float4 lo = dst[0], hi = dst[1];
+        lo.x += total[0] * share; lo.y += total[1] * share; lo.z += total[2] * share; lo.w += total[3] * share;
+        hi.x += total[4] * share; hi.y += total[5] * share; hi.z += total[6] * share; hi.w += total[7] * share;
+        dst[0] = lo;
+        dst[1] = hi;
+    }
+}
+
+template <typename T>
+bool launch_normed_rows(float* residual, const Branches<T>& b, int count, int tokens, int hidden,
+                        float eps, cudaStream_t stream) {
+    bool aligned = hidden % 8 == 0 && hidden <= 8192 && (reinterpret_cast<uintptr_t>(residual) & 15) == 0;
+    for (int i = 0; i < count; ++i)
+        aligned = aligned && (reinterpret_cast<uintptr_t>(b.x[i]) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(b.weight[i]) & 15) == 0;
+    if (!aligned || count < 1 || count > 2) return false;
+    const int groups = hidden / 8;
+    const int iter = groups > 512 ? 2 : 1;
+    const int threads = ((groups + iter - 1) / iter + 31) / 32 * 32;
+#define ROWS_KERNEL(COUNT, ITER)                                                              \
+    launch_kernel(normed_mean_add_rows_kernel<T, COUNT, ITER>, dim3(tokens), dim3(threads), 0, \
+                  stream, true, residual, b, hidden, eps)
+    if (count == 1 && iter == 1) ROWS_KERNEL(1, 1);
+    else if (count == 1) ROWS_KERNEL(1, 2);
+    else if (iter == 1) ROWS_KERNEL(2, 1);
+    else ROWS_KERNEL(2, 2);
+#undef ROWS_KERNEL
+    return true;
+}
+
 MLXONE_API int mlxone_normed_mean_add(float* residual, const void* const* x,
                                       const float* const* weight, int count, int tokens, int hidden,
                                       float eps, int dtype, cudaStream_t stream) {
@@ -161,11 +252,13 @@ MLXONE_API int mlxone_normed_mean_add(float* residual, const void* const* x,
     if (dtype == MLXONE_BF16) {
         Branches<__nv_bfloat16> b = {};
         for (int i = 0; i < count; ++i) { b.x[i] = (const __nv_bfloat16*)x[i]; b.weight[i] = weight[i]; }
+        if (!launch_normed_rows<__nv_bfloat16>(residual, b, count, tokens, hidden, eps, stream))
         launch_kernel(normed_mean_add_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
                       true, residual, b, count, hidden, eps);
     } else {
         Branches<float> b = {};
         for (int i = 0; i < count; ++i) { b.x[i] = (const float*)x[i]; b.weight[i] = weight[i]; }
+        if (!launch_normed_rows<float>(residual, b, count, tokens, hidden, eps, stream))
         launch_kernel(normed_mean_add_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true,
                       residual, b, count, hidden, eps);
     }

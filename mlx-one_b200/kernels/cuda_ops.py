@@ -130,6 +130,13 @@ class CudaOps:
             raise KernelError(self.lib.mlxone_last_error().decode())
         self.launches += 1
 
+    def _need_rows(self, tensor: torch.Tensor, dtype: torch.dtype, what: str) -> None:
+        """Rows whose values lie together; the rows themselves may be a slice of a wider matrix."""
+        if (tensor.dtype != dtype or tensor.dim() != 2 or tensor.stride(1) != 1
+                or tensor.device != self.device):
+            raise KernelError(f"{what} must be {dtype} rows on {self.device}, got {tensor.dtype} "
+                              f"{tuple(tensor.shape)} with strides {tensor.stride()} on {tensor.device}")
+
     def _need(self, tensor: torch.Tensor, dtype: torch.dtype, what: str) -> None:
         if tensor.dtype != dtype or not tensor.is_contiguous() or tensor.device != self.device:
             raise KernelError(f"{what} must be a contiguous {dtype} tensor on {self.device}, got "
@@ -207,6 +214,7 @@ class CudaOps:
 
     # epilogues of the skinny product
     _STORE, _SWIGLU, _ADD, _STORE_F32 = 0, 1, 2, 3
+    _ACTIVATE = 16          # + the activation's code: a bfloat16 store of the activated product
 
     def _skinny(self, a, w, fused=False) -> bool:
         """Whether a[M, K] @ w[N, K]^T goes to the weight-streaming kernel: bfloat16, few rows,
@@ -404,7 +412,21 @@ class CudaOps:
         return out
 
     def linear_act(self, a, w, kind):
-        """act(a @ w^T): the product followed by the activation kernel."""
+        """act(a @ w^T): for few rows the activation is the skinny product's epilogue (also with
+        the norm of its input applied while loading); else the product, then the activation
+        kernel."""
+        if kind not in self.ACTIVATIONS:
+            raise KernelError(f"unknown activation {kind!r}")
+        epilogue = self._ACTIVATE + self.ACTIVATIONS[kind]
+        if isinstance(a, NormedInput):
+            out = torch.empty((a.shape[0], w.shape[0]), dtype=a.dtype, device=self.device)
+            self._normed_call(a, w, None, out, w.shape[0], epilogue)
+            return out
+        self._check_product(a, w)
+        if self._skinny(a, w, fused=True):
+            out = torch.empty((a.shape[0], w.shape[0]), dtype=a.dtype, device=self.device)
+            self._skinny_call(a, w, None, out, w.shape[0], epilogue)
+            return out
         return self.activation(self.linear(a, w), kind)
 
     # ---- the 32-bit stream
@@ -459,9 +481,10 @@ class CudaOps:
         """From the fused projection [tokens, q | k | v | gate | beta | decay] to the mixer's
         gated output [tokens, heads * value_dim]: convolutions with silu, unit-length queries
         and keys, the recurrence over each request's tokens on its 32-bit state, the output's
-        norm and gate. The state slot holds the heads' matrices and the convolutions' inputs."""
+        norm and gate. The state slot holds the heads' matrices and a ring of the convolutions'
+        inputs (row position % taps)."""
         tokens = projected.shape[0]
-        self._need(projected, projected.dtype, "projected")
+        self._need_rows(projected, projected.dtype, "projected")
         qk, inner = kv_heads * key_dim, heads * value_dim
         if projected.shape[1] != 2 * qk + 2 * inner + 2 * heads:
             raise KernelError("the projection's width does not match the head counts")
@@ -471,6 +494,8 @@ class CudaOps:
         size = self.lib.mlxone_gated_delta_state(heads, kv_heads, key_dim, value_dim, taps)
         if view.state[0].numel() != size:
             raise KernelError(f"a state slot has {view.state[0].numel()} values, the mixer needs {size}")
+        # a step of single tokens runs as one kernel, else preparation, scan and finish
+        single = ctx.max_portion == 1 and tokens == ctx.requests
         scratch = torch.empty(self.lib.mlxone_gated_delta_scratch(tokens, heads, kv_heads, key_dim,
                                                                   value_dim),
                               dtype=torch.float32, device=self.device)
@@ -483,8 +508,10 @@ class CudaOps:
                    _c_void_p(_ptr(scratch)), _c_void_p(_ptr(out)), _c_int(tokens),
                    _c_int(ctx.requests), _c_int(heads), _c_int(kv_heads), _c_int(key_dim),
                    _c_int(value_dim), _c_int(taps), _c_int(1 if write else 0),
+                   _c_int(projected.stride(0)), _c_int(1 if single else 0),
                    _c_int(_dtype_code(projected.dtype)))
-        self.launches += 2
+        if not (single and value_dim <= 128):
+            self.launches += 2
         return out
 
     def swiglu(self, gate_up):
@@ -562,11 +589,15 @@ class CudaOps:
         select the general kernel, which pads queries, keys and values with zeros to the
         pages' row size."""
         tokens = qkv.shape[0]
-        self._need(qkv, view.kv.dtype, "qkv")
         inv_freq, rotary_dim = (None, 0) if rotary is None else rotary
         row_dim = view.kv.shape[-1]
         value_dim = value_dim or head_dim
-        if value_dim != head_dim or row_dim != head_dim or amplitude != 1.0 or norm_after:
+        general = value_dim != head_dim or row_dim != head_dim or amplitude != 1.0 or norm_after
+        if general:
+            self._need_rows(qkv, view.kv.dtype, "qkv")
+        else:
+            self._need(qkv, view.kv.dtype, "qkv")
+        if general:
             if qkv.shape[1] != (heads + kv_heads) * head_dim + kv_heads * value_dim:
                 raise KernelError("qkv width does not match the head counts")
             if norm_after and eps is None:
@@ -582,7 +613,8 @@ class CudaOps:
                        _c_int(view.block_table.shape[1]), _c_int(view.page_size),
                        _c_int(view.kv.shape[1]), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
                        _c_int(head_dim), _c_int(value_dim), _c_int(row_dim),
-                       _c_int(1 if write else 0), _c_int(_dtype_code(qkv.dtype)),
+                       _c_int(1 if write else 0), _c_int(qkv.stride(0)),
+                       _c_int(_dtype_code(qkv.dtype)),
                        _c_void_p(_ptr(self.error_flag)))
             return q
         if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:

@@ -183,8 +183,21 @@ class Mixer(Part):
 
     @classmethod
     def cache_need(cls, spec: PartSpec):
-        """``PagedKeyValues``, ``FixedState`` or None."""
+        """``PagedKeyValues``, ``FixedState`` or None; or, for a mixer made of several mixers, a
+        mapping name -> need (``forward`` then gets a mapping name -> view as ``cache``)."""
         return None
+
+    def input_projection(self):
+        """(weight [n, hidden], bias float32 [n] or None) if everything this mixer reads of its
+        input is that one product, and ``forward_projected`` takes its result as rows that may
+        be a slice of a wider matrix; else None. Several such mixers on one input share one
+        product."""
+        return None
+
+    def forward_projected(self, projected: torch.Tensor, ctx: "StepContext", cache: Any,
+                          write: bool, residual=None):
+        """``forward`` from the input projection's result on."""
+        raise NotImplementedError
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Any, write: bool):
         """x: normed input [tokens, hidden] in the compute dtype. Returns the mixer's

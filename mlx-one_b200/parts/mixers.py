@@ -114,8 +114,15 @@ class Attention(Mixer):
     def inner_parts(self):
         return (self.position,)
 
+    def input_projection(self):
+        # (the plain form's kernels want rows of their own, the general preparation takes slices)
+        return (self.qkv, self.qkv_bias) if self.extra else None
+
     def forward(self, x, ctx, cache, write, residual=None):
-        qkv = self.ops.linear(x, self.qkv, self.qkv_bias)
+        return self.forward_projected(self.ops.linear(x, self.qkv, self.qkv_bias), ctx, cache,
+                                      write, residual)
+
+    def forward_projected(self, qkv, ctx, cache, write, residual=None):
         mixed = self.ops.qkv_attention(
             qkv, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm, k_weight=self.k_norm, eps=self.eps,
@@ -192,7 +199,8 @@ class GatedDeltaRule(Mixer):
     token and head: S = g S; u = beta (v - S^T k); S = S + k u^T; o = S^T q. The output is
     o / rms(o) (over value_dim, with ``eps``) * norm * silu(W_g x), projected by W_o.
     Everything after the convolutions' silu is 32-bit. The state of a request is S of every
-    head and the last taps - 1 inputs of every convolution, in one 32-bit slot."""
+    head and the last inputs of every convolution (a ring of ``taps`` rows, row = position %
+    taps, of which a step reads the taps - 1 before its own), in one 32-bit slot."""
 
     UNIT_EPS = 1e-6
 
@@ -219,7 +227,7 @@ class GatedDeltaRule(Mixer):
     def state_size(cls, spec):
         qk, inner = cls._channels(spec)
         matrices = spec["heads"] * spec["key_dim"] * spec["value_dim"]
-        return matrices + (spec["taps"] - 1) * (2 * qk + inner)
+        return matrices + spec["taps"] * (2 * qk + inner)
 
     @classmethod
     def cache_need(cls, spec):
@@ -245,8 +253,13 @@ class GatedDeltaRule(Mixer):
     fuses_residual = True
     accepts_normed_input = True
 
+    def input_projection(self):
+        return self.project, None
+
     def forward(self, x, ctx, cache, write, residual=None):
-        projected = self.ops.linear(x, self.project)
+        return self.forward_projected(self.ops.linear(x, self.project), ctx, cache, write, residual)
+
+    def forward_projected(self, projected, ctx, cache, write, residual=None):
         mixed = self.ops.gated_delta_rule(
             projected, conv=self.conv, a_log=self.a_log, dt_bias=self.dt_bias,
             norm_weight=self.norm, eps=self.eps, unit_eps=self.UNIT_EPS, ctx=ctx, view=cache,
@@ -259,7 +272,8 @@ class GatedDeltaRule(Mixer):
 @MIXERS.register("parallel")
 class ParallelMixers(Mixer):
     """Several mixers side by side on the same input. Parameters: ``hidden``, ``eps``,
-    ``branches``: a tuple of (name, mixer PartSpec, stored name of the branch's output weight).
+    ``branches``: a tuple of (name, mixer PartSpec, stored name of the branch's output weight);
+    ``shared_projection`` (True): one product for the input projections of all branches.
     Every branch's output is divided by its root mean square over the model width (with
     ``eps``) and multiplied by its weight [hidden]; the mixer's output is the mean of these,
     added to the 32-bit stream without being rounded first. Each branch keeps what its mixer
@@ -293,6 +307,28 @@ class ParallelMixers(Mixer):
             self.names.append(name)
             self.branches.append(kind(part, local, runtime))
             self.weights.append(self.vector(tensors[weight]))
+        # One product for all branches where each reads its input through one projection: the
+        # weights stacked, the branches take column ranges of the result. The input is then used
+        # by that product only, so the norm before it may be applied inside it.
+        self.project = self.project_bias = None
+        self.columns: list[tuple[int, int]] = []
+        projections = [branch.input_projection() for branch in self.branches]
+        if spec.get("shared_projection", True) and all(p is not None for p in projections):
+            self.project = torch.cat([weight for weight, _ in projections], dim=0).contiguous()
+            if any(bias is not None for _, bias in projections):
+                self.project_bias = torch.cat([
+                    bias if bias is not None else torch.zeros(weight.shape[0], dtype=torch.float32,
+                                                              device=weight.device)
+                    for weight, bias in projections]).contiguous()
+            at = 0
+            for weight, _ in projections:
+                self.columns.append((at, at + weight.shape[0]))
+                at += weight.shape[0]
+            for branch in self.branches:        # the stacked copy is the one that is read
+                for name in ("qkv", "project"):
+                    if hasattr(branch, name):
+                        setattr(branch, name, None)
+            self.accepts_normed_input = True
 
     fuses_residual = True
 
@@ -304,8 +340,13 @@ class ParallelMixers(Mixer):
 
     def forward(self, x, ctx, cache, write, residual=None):
         cache = cache or {}
-        outputs = [branch.forward(x, ctx, cache.get(name), write)
-                   for name, branch in zip(self.names, self.branches)]
+        if self.project is not None:
+            projected = self.ops.linear(x, self.project, self.project_bias)
+            outputs = [branch.forward_projected(projected[:, lo:hi], ctx, cache.get(name), write)
+                       for name, branch, (lo, hi) in zip(self.names, self.branches, self.columns)]
+        else:
+            outputs = [branch.forward(x, ctx, cache.get(name), write)
+                       for name, branch in zip(self.names, self.branches)]
         if residual is None:
             raise ValueError("side-by-side mixers add their mean into the stream themselves")
         self.ops.normed_mean_add(residual, outputs, self.weights, self.eps)

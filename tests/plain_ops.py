@@ -205,10 +205,10 @@ class PlainOps:
             n = last - first
             slot = view.state[slots[r]]
             state = slot[:matrices].view(heads, key_dim, value_dim).clone()
-            tail = slot[matrices:].view(max(taps - 1, 0), channels).clone()
-            if taps > 1:
-                valid = torch.arange(taps - 1) + history[r] - (taps - 1) >= 0
-                tail = tail * valid[:, None]
+            ring = slot[matrices:].view(taps, channels)        # row p % taps: input at position p
+            before = [history[r] - (taps - 1) + s for s in range(taps - 1)]
+            tail = torch.stack([ring[p % taps] if p >= 0 else torch.zeros(channels) for p in before]) \
+                if taps > 1 else torch.zeros(0, channels)
             padded = torch.cat((tail, flat[first:last, :channels]), dim=0)
             mixed = sum(padded[j:j + n] * conv[:, j] for j in range(taps))
             mixed = silu(mixed)
@@ -226,8 +226,8 @@ class PlainOps:
                 state[h] = s
             if write:
                 slot[:matrices] = state.reshape(-1)
-                if taps > 1:
-                    slot[matrices:] = padded[n:n + taps - 1].reshape(-1)
+                for index in range(max(n - taps, 0), n):
+                    ring[(history[r] + index) % taps] = flat[first + index, :channels]
         out = out * torch.rsqrt(out.pow(2).mean(dim=-1, keepdim=True) + eps) * norm_weight
         out = out * silu(gate)
         return out.reshape(tokens, inner).to(projected.dtype)

@@ -120,7 +120,7 @@ def test_weight_contract_and_cache_entries():
     assert len(needs) == 10
     assert needs[(0, "left")] == PagedKeyValues(2, 32, None)       # rows of max(32, 16)
     assert needs[(4, "left")] == PagedKeyValues(1, 16, None)
-    assert needs[(0, "right")] == FixedState((4 * 16 * 24 + 3 * (2 * 32 + 96),), "float32")
+    assert needs[(0, "right")] == FixedState((4 * 16 * 24 + 4 * (2 * 32 + 96),), "float32")
 
 
 def test_stretched_frequencies():

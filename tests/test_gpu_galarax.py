@@ -224,9 +224,10 @@ def test_gated_delta_rule_alone(ops, dtype, sizes):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_stream_operations(ops, dtype):
+@pytest.mark.parametrize("hidden", [200, 203, 4104])
+def test_stream_operations(ops, dtype, hidden):
     generator = torch.Generator().manual_seed(3)
-    tokens, hidden, vocab = 37, 200, 50
+    tokens, vocab = 37, 50
     residual = torch.randn(tokens, hidden, generator=generator)
     delta = torch.randn(tokens, hidden, generator=generator).to(dtype)
     table = torch.randn(vocab, hidden, generator=generator).to(dtype)
