@@ -158,8 +158,9 @@ delta_scan_kernel(const float* __restrict__ q_in, const float* __restrict__ k_in
     constexpr int ROWS = PER * LANES;                 // rows of S a thread group covers (>= D)
     constexpr int COLUMNS = SCAN_THREADS / LANES;     // columns of S per block
     constexpr int BUFFER = CHUNK * (2 * ROWS + COLUMNS + 3);
+    constexpr int GROUP = 4;                          // tokens worked on together
     extern __shared__ __align__(16) float staged[];
-    griddep_launch();
+    __shared__ float gram[CHUNK / GROUP][2][GROUP][GROUP];   // k_i.k_t and k_i.q_t, i < t in a group
     griddep_wait();
     const int r = blockIdx.z;
     const int first = request_start[r], last = request_start[r + 1];
@@ -167,6 +168,7 @@ delta_scan_kernel(const float* __restrict__ q_in, const float* __restrict__ k_in
     float* slot = state + (size_t)slots[r] * sizes.state();
     if (blockIdx.y == H) {
         // the inputs of the portion's last positions (at most taps of them) go into the ring
+        griddep_launch();
         if (!write) return;
         const int channels = sizes.channels(), taps = sizes.taps;
         const int n = last - first, kept = min(n, taps);
@@ -216,6 +218,11 @@ delta_scan_kernel(const float* __restrict__ q_in, const float* __restrict__ k_in
             copy_async_4(cs + threadIdx.x, coef + at * 2);
             copy_async_4(cs + CHUNK + threadIdx.x, coef + at * 2 + 1);
             copy_async_4(cs + 2 * CHUNK + threadIdx.x, kq + (size_t)(base + threadIdx.x) * G + g);
+        } else if (threadIdx.x < CHUNK) {
+            // places behind the portion's end: a token that changes nothing (g = 1, beta = 0)
+            cs[threadIdx.x] = 1.f;
+            cs[CHUNK + threadIdx.x] = 0.f;
+            cs[2 * CHUNK + threadIdx.x] = 0.f;
         }
         copy_commit();
     };
@@ -234,37 +241,104 @@ delta_scan_kernel(const float* __restrict__ q_in, const float* __restrict__ k_in
         const float* qs = ks + CHUNK * ROWS;
         const float* vs = qs + CHUNK * ROWS;
         const float* cs = vs + CHUNK * COLUMNS;
-        for (int t = 0; t < count; ++t) {
-            float k[PER];
-            float wk[4] = {0.f, 0.f, 0.f, 0.f}, wq[4] = {0.f, 0.f, 0.f, 0.f};
+        // the products k_i.k_t and k_i.q_t of the pairs i < t inside each group of four tokens:
+        // 4 groups x 6 pairs x 2 kinds, each by LANES lanes
+        for (int item = threadIdx.x / LANES; item < (CHUNK / GROUP) * 12; item += SCAN_THREADS / LANES) {
+            const int group = item / 12, kind = (item % 12) / 6, pair = item % 6;
+            const int t = pair < 1 ? 1 : (pair < 3 ? 2 : 3);
+            const int i = pair - (t == 1 ? 0 : (t == 2 ? 1 : 3));
+            const float* left = ks + (group * GROUP + i) * ROWS;
+            const float* right = (kind ? qs : ks) + (group * GROUP + t) * ROWS;
+            float dot = 0.f;
 #pragma unroll
             for (int e = 0; e < PER; e += 4) {
-                const int at = t * ROWS + (e / 4) * (4 * LANES) + lane * 4;
-                const float4 k4 = *reinterpret_cast<const float4*>(ks + at);
-                const float4 q4 = *reinterpret_cast<const float4*>(qs + at);
-                k[e] = k4.x; k[e + 1] = k4.y; k[e + 2] = k4.z; k[e + 3] = k4.w;
-                wk[0] = fmaf(S[e], k4.x, wk[0]); wq[0] = fmaf(S[e], q4.x, wq[0]);
-                wk[1] = fmaf(S[e + 1], k4.y, wk[1]); wq[1] = fmaf(S[e + 1], q4.y, wq[1]);
-                wk[2] = fmaf(S[e + 2], k4.z, wk[2]); wq[2] = fmaf(S[e + 2], q4.z, wq[2]);
-                wk[3] = fmaf(S[e + 3], k4.w, wk[3]); wq[3] = fmaf(S[e + 3], q4.w, wq[3]);
+                const int at = (e / 4) * (4 * LANES) + lane * 4;
+                const float4 x = *reinterpret_cast<const float4*>(left + at);
+                const float4 y = *reinterpret_cast<const float4*>(right + at);
+                dot = fmaf(x.x, y.x, dot); dot = fmaf(x.y, y.y, dot);
+                dot = fmaf(x.z, y.z, dot); dot = fmaf(x.w, y.w, dot);
             }
-            float with_k = (wk[0] + wk[1]) + (wk[2] + wk[3]);
-            float with_q = (wq[0] + wq[1]) + (wq[2] + wq[3]);
+#pragma unroll
+            for (int across = 1; across < LANES; across <<= 1)
+                dot += __shfl_xor_sync(0xffffffffu, dot, across);
+            if (lane == 0) gram[group][kind][i][t] = dot;
+        }
+        __syncthreads();
+        for (int t0 = 0; t0 < count; t0 += GROUP) {
+            // the sums of this column (as it stands before the group) with the four k and q
+            float a[GROUP] = {0.f, 0.f, 0.f, 0.f}, b[GROUP] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int e = 0; e < PER; e += 4) {
+                const int at = (e / 4) * (4 * LANES) + lane * 4;
+#pragma unroll
+                for (int j = 0; j < GROUP; ++j) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + (t0 + j) * ROWS + at);
+                    const float4 q4 = *reinterpret_cast<const float4*>(qs + (t0 + j) * ROWS + at);
+                    a[j] = fmaf(S[e], k4.x, a[j]); b[j] = fmaf(S[e], q4.x, b[j]);
+                    a[j] = fmaf(S[e + 1], k4.y, a[j]); b[j] = fmaf(S[e + 1], q4.y, b[j]);
+                    a[j] = fmaf(S[e + 2], k4.z, a[j]); b[j] = fmaf(S[e + 2], q4.z, b[j]);
+                    a[j] = fmaf(S[e + 3], k4.w, a[j]); b[j] = fmaf(S[e + 3], q4.w, b[j]);
+                }
+            }
 #pragma unroll
             for (int across = 1; across < LANES; across <<= 1) {
-                with_k += __shfl_xor_sync(0xffffffffu, with_k, across);
-                with_q += __shfl_xor_sync(0xffffffffu, with_q, across);
-            }
-            const float decay = cs[t];
-            const float u = cs[CHUNK + t] * (vs[t * COLUMNS + local] - decay * with_k);
 #pragma unroll
-            for (int e = 0; e < PER; ++e) S[e] = fmaf(k[e], u, decay * S[e]);
-            if (live && lane == 0)
-                out[((size_t)(base + t) * H + h) * V + column] =
-                    fmaf(u, cs[2 * CHUNK + t], decay * with_q);
+                for (int j = 0; j < GROUP; ++j) {
+                    a[j] += __shfl_xor_sync(0xffffffffu, a[j], across);
+                    b[j] += __shfl_xor_sync(0xffffffffu, b[j], across);
+                }
+            }
+            // token by token with numbers only. With s_j the column after token j of the group and
+            // c(i, j) = g_(i+1) ... g_(j-1):  s_(j-1).x = g_1 .. g_(j-1) (s_0.x) + sum_(i<j) c(i, j) (k_i.x) u_i
+            const int group = t0 / GROUP;
+            float decay[GROUP], u[GROUP];
+#pragma unroll
+            for (int j = 0; j < GROUP; ++j) decay[j] = cs[t0 + j];
+            float before = 1.f;                       // g_1 ... g_(j-1)
+#pragma unroll
+            for (int j = 0; j < GROUP; ++j) {
+                float with_k = before * a[j], with_q = before * b[j];
+                float carry = 1.f;                    // c(i, j), from i = j - 1 downwards
+#pragma unroll
+                for (int i = j - 1; i >= 0; --i) {
+                    with_k = fmaf(carry * gram[group][0][i][j], u[i], with_k);
+                    with_q = fmaf(carry * gram[group][1][i][j], u[i], with_q);
+                    carry *= decay[i];
+                }
+                u[j] = cs[CHUNK + t0 + j] * (vs[(t0 + j) * COLUMNS + local] - decay[j] * with_k);
+                if (live && lane == 0 && t0 + j < count)
+                    out[((size_t)(base + t0 + j) * H + h) * V + column] =
+                        fmaf(u[j], cs[2 * CHUNK + t0 + j], decay[j] * with_q);
+                before *= decay[j];
+            }
+            // s_4 = g_1 .. g_4 s_0 + sum_i (g_(i+1) .. g_4) k_i u_i
+            float weight[GROUP];
+            float after = 1.f;
+#pragma unroll
+            for (int j = GROUP - 1; j >= 0; --j) {
+                weight[j] = u[j] * after;
+                after *= decay[j];
+            }
+#pragma unroll
+            for (int e = 0; e < PER; e += 4) {
+                const int at = (e / 4) * (4 * LANES) + lane * 4;
+                float next[4] = {after * S[e], after * S[e + 1], after * S[e + 2], after * S[e + 3]};
+#pragma unroll
+                for (int j = 0; j < GROUP; ++j) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(ks + (t0 + j) * ROWS + at);
+                    next[0] = fmaf(k4.x, weight[j], next[0]);
+                    next[1] = fmaf(k4.y, weight[j], next[1]);
+                    next[2] = fmaf(k4.z, weight[j], next[2]);
+                    next[3] = fmaf(k4.w, weight[j], next[3]);
+                }
+                S[e] = next[0]; S[e + 1] = next[1]; S[e + 2] = next[2]; S[e + 3] = next[3];
+            }
         }
         __syncthreads();          // the buffer is fetched into again two rounds on
     }
+    // the kernels behind this one may start now: earlier they would sit on the SMs beside a
+    // kernel that runs long on few warps
+    griddep_launch();
     if (write && live) {
 #pragma unroll
         for (int e = 0; e < PER; ++e) {

@@ -222,8 +222,9 @@ qk_prep_general_kernel(const T* __restrict__ qkv, const float* __restrict__ q_we
                        int page_size, long long kv_half, int tokens, int heads, int kv_heads,
                        int head_dim, int value_dim, int row_dim, int write_kv, int ld,
                        int* __restrict__ error_flag) {
-    // One block per token: the angles' cosines and sines are worked out once for all its heads
-    // (rotary_dim / 2 of each, scaled), then the warps take the token's heads in turn.
+    // Blocks (token, part): the angles' cosines and sines are worked out once for the block's
+    // heads (rotary_dim / 2 of each, scaled), then its warps take their share of the token's
+    // heads in turn: a warp has one head in a step of few tokens, two in a large one.
     extern __shared__ float shared[];
     float* cosines = shared;
     float* sines = shared + rotary_dim / 2;
@@ -256,7 +257,7 @@ qk_prep_general_kernel(const T* __restrict__ qkv, const float* __restrict__ q_we
         }
     }
     float* values = shared + rotary_dim + warp * row_dim;
-    for (int slot = warp; slot < slots_per_token; slot += WARPS) {
+    for (int slot = warp + WARPS * blockIdx.y; slot < slots_per_token; slot += WARPS * gridDim.y) {
         const bool is_q = slot < heads;
         const bool is_k = !is_q && slot < heads + kv_heads;
         if (!is_q && page_base == nullptr) continue;
@@ -395,19 +396,21 @@ MLXONE_API int mlxone_qk_prep_general(const void* qkv, const float* q_weight, co
     MLXONE_REQUIRE(ld >= (heads + kv_heads) * head_dim + kv_heads * value_dim,
                    "qk_prep: rows %d apart are shorter than their heads", ld);
     MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0, "qk_prep: bad page geometry");
-    const int blocks = tokens;
+    const int slots = heads + 2 * kv_heads;
+    const int parts = tokens < 64 ? ceil_div_host(slots, WARPS) : ceil_div_host(slots, 2 * WARPS);
+    const dim3 blocks(tokens, parts < 1 ? 1 : parts);
     const size_t shared = (size_t)(rotary_dim + WARPS * row_dim) * sizeof(float);
     const long long kv_half = (long long)pages * kv_heads * page_size * row_dim;
     if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
-        launch_kernel(qk_prep_general_kernel<T>, dim3(blocks), dim3(WARPS * 32), shared, stream, true,
+        launch_kernel(qk_prep_general_kernel<T>, blocks, dim3(WARPS * 32), shared, stream, true,
                       (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, amplitude,
                       norm_mode, positions, token_request, (T*)q_out, (T*)kv, block_table,
                       table_width, page_size, kv_half, tokens, heads, kv_heads, head_dim, value_dim,
                       row_dim, write_kv, ld, error_flag);
     } else {
         using T = float;
-        launch_kernel(qk_prep_general_kernel<T>, dim3(blocks), dim3(WARPS * 32), shared, stream, true,
+        launch_kernel(qk_prep_general_kernel<T>, blocks, dim3(WARPS * 32), shared, stream, true,
                       (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, amplitude,
                       norm_mode, positions, token_request, (T*)q_out, (T*)kv, block_table,
                       table_width, page_size, kv_half, tokens, heads, kv_heads, head_dim, value_dim,
