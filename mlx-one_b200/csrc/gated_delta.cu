@@ -19,11 +19,13 @@
 //            A column of S depends on no other column, so columns are spread over threads and
 //            blocks; a column's D values are spread over eight lanes of a warp. With the dot
 //            products of the column with k and q taken before the update,
-//            u = beta (v - g (S.k)) and o = g (S.q) + u (k.q): one pass reads the column for both
-//            sums (four partial sums each, so that no chain of additions is longer than a
-//            quarter of the lane's values) and a second one updates it. The operands of the
-//            next 16 tokens travel to shared memory (cp.async) while the current 16 are worked
-//            on. Extra blocks write the convolution's inputs into the ring.
+//            u = beta (v - g (S.k)) and o = g (S.q) + u (k.q). Four tokens are worked on
+//            together: one pass takes the sums of the column, as it stands before the four,
+//            with their k and q; with the products k_i.k_j and k_i.q_j of the four (worked out
+//            once per block) the four u and o follow from numbers alone; a second pass updates
+//            the column for all four. The operands of the next 16 tokens travel to shared
+//            memory (cp.async) while the current 16 are worked on. Extra blocks write the
+//            convolution's inputs into the ring.
 //   finish   per (token, head): o / rms(o) * weight * silu(gate), in the compute type.
 // A step of single tokens runs one kernel, a block per (request, value head): the head's
 // matrix is asked for before the wait for the projection, the convolutions, norms and gates of
@@ -47,6 +49,10 @@ __device__ __forceinline__ void copy_async_4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(to), "l"(src) : "memory");
 }
 __device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copy_async_16(float* dst, const float* src) {
+    const uint32_t to = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(to), "l"(src) : "memory");
+}
 template <int N>
 __device__ __forceinline__ void copy_wait_for() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -192,6 +198,10 @@ delta_scan_kernel(const float* __restrict__ q_in, const float* __restrict__ k_in
         const int row = (e / 4) * (4 * LANES) + lane * 4 + e % 4;
         S[e] = live && row < D ? matrix[(size_t)row * V + column] : 0.f;
     }
+    // whether k, q and v rows can travel 16 bytes at a time
+    const bool quads = D % 4 == 0 && V % 4 == 0 &&
+                       ((reinterpret_cast<uintptr_t>(q_in) | reinterpret_cast<uintptr_t>(k_in) |
+                         reinterpret_cast<uintptr_t>(v_in)) & 15) == 0;
     // rows behind D and columns behind V stay zero in both buffers
     for (int i = threadIdx.x; i < 2 * BUFFER; i += SCAN_THREADS) staged[i] = 0.f;
     __syncthreads();
@@ -201,17 +211,36 @@ delta_scan_kernel(const float* __restrict__ q_in, const float* __restrict__ k_in
         float* qs = ks + CHUNK * ROWS;
         float* vs = qs + CHUNK * ROWS;
         float* cs = vs + CHUNK * COLUMNS;
-        for (int i = threadIdx.x; i < count * D; i += SCAN_THREADS) {
-            const int t = i / D, e = i % D;
-            const size_t at = ((size_t)(base + t) * G + g) * D + e;
-            copy_async_4(ks + t * ROWS + e, k_in + at);
-            copy_async_4(qs + t * ROWS + e, q_in + at);
-        }
         const int wide = min(COLUMNS, V - (int)blockIdx.x * COLUMNS);
-        for (int i = threadIdx.x; i < count * wide; i += SCAN_THREADS) {
-            const int t = i / wide, c = i % wide;
-            copy_async_4(vs + t * COLUMNS + c,
-                         v_in + ((size_t)(base + t) * H + h) * V + blockIdx.x * COLUMNS + c);
+        if (quads) {
+            // rows of a multiple of four values: 16 bytes a copy
+            const int per_row = D / 4;
+            const bool power = (per_row & (per_row - 1)) == 0;
+            const int shift = __ffs(per_row) - 1;
+            for (int i = threadIdx.x; i < count * per_row; i += SCAN_THREADS) {
+                const int t = power ? i >> shift : i / per_row;
+                const int e = (i - t * per_row) * 4;
+                const size_t at = ((size_t)(base + t) * G + g) * D + e;
+                copy_async_16(ks + t * ROWS + e, k_in + at);
+                copy_async_16(qs + t * ROWS + e, q_in + at);
+            }
+            for (int i = threadIdx.x; i < count * (wide / 4); i += SCAN_THREADS) {
+                const int t = i / (wide / 4), c = (i % (wide / 4)) * 4;
+                copy_async_16(vs + t * COLUMNS + c,
+                              v_in + ((size_t)(base + t) * H + h) * V + blockIdx.x * COLUMNS + c);
+            }
+        } else {
+            for (int i = threadIdx.x; i < count * D; i += SCAN_THREADS) {
+                const int t = i / D, e = i % D;
+                const size_t at = ((size_t)(base + t) * G + g) * D + e;
+                copy_async_4(ks + t * ROWS + e, k_in + at);
+                copy_async_4(qs + t * ROWS + e, q_in + at);
+            }
+            for (int i = threadIdx.x; i < count * wide; i += SCAN_THREADS) {
+                const int t = i / wide, c = i % wide;
+                copy_async_4(vs + t * COLUMNS + c,
+                             v_in + ((size_t)(base + t) * H + h) * V + blockIdx.x * COLUMNS + c);
+            }
         }
         if (threadIdx.x < count) {
             const size_t at = (size_t)(base + threadIdx.x) * H + h;
@@ -549,24 +578,35 @@ int launch_delta(const void* projected, const float* conv, const float* a_log, c
                   (const T*)projected, conv, a_log, dt_bias, (const float*)state, slots,
                   token_request, request_start, history, q, k, v, coef, kq, sizes, unit_eps, ld);
     MLXONE_LAUNCH_CHECK("gated delta rule (prepare)");
-    constexpr int LANES = 8;
-    constexpr int COLUMNS = SCAN_THREADS / LANES;
-    const dim3 grid(ceil_div_host(V, COLUMNS), H + 1, requests);
-#define SCAN(PER)                                                                                \
-    do {                                                                                         \
+    // A column's values are spread over 8 lanes (16 for keys longer than 128). Measured at 16 heads
+    // of 128 x 128 and 2048 tokens: with 16 lanes every lane repeats the four tokens' solve for
+    // half as many values of its own, 292 M warp instructions and 702 us.
+#define SCAN(PER, LANES)                                                                          \
+    do {                                                                                          \
+        constexpr int COLUMNS = SCAN_THREADS / LANES;                                             \
+        const dim3 grid(ceil_div_host(V, COLUMNS), H + 1, requests);                              \
         const size_t staged = (size_t)2 * CHUNK * (2 * PER * LANES + COLUMNS + 3) * sizeof(float); \
-        if (staged > 48 * 1024)                                                                  \
-            cudaFuncSetAttribute(delta_scan_kernel<T, PER, LANES>,                               \
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged);      \
+        if (staged > 48 * 1024)                                                                   \
+            cudaFuncSetAttribute(delta_scan_kernel<T, PER, LANES>,                                \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged);       \
         launch_kernel(delta_scan_kernel<T, PER, LANES>, grid, dim3(SCAN_THREADS), staged, stream, \
-                      true, (const float*)q, (const float*)k, (const float*)v,                   \
-                      (const float*)coef, (const float*)kq, (const T*)projected, state, slots,   \
-                      request_start, history, o, sizes, write, ld);                              \
+                      true, (const float*)q, (const float*)k, (const float*)v,                    \
+                      (const float*)coef, (const float*)kq, (const T*)projected, state, slots,    \
+                      request_start, history, o, sizes, write, ld);                               \
     } while (0)
-    if (D <= 32) SCAN(4);
-    else if (D <= 64) SCAN(8);
-    else if (D <= 128) SCAN(16);
-    else SCAN(32);
+    // ... and so does 8 lanes when its blocks fill the SMs (156 M instructions, 536 us); with
+    // fewer blocks than half the SMs, 16 lanes make twice as many.
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
+    }
+    const bool few = (long long)requests * H * ceil_div_host(V, SCAN_THREADS / 8) * 2 <= sm_count;
+    if (D <= 32) SCAN(4, 8);
+    else if (D <= 64) { if (few) SCAN(4, 16); else SCAN(8, 8); }
+    else if (D <= 128) { if (few) SCAN(8, 16); else SCAN(16, 8); }
+    else SCAN(16, 16);
 #undef SCAN
     MLXONE_LAUNCH_CHECK("gated delta rule (scan)");
     const long long items = (long long)tokens * H;
