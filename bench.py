@@ -1066,6 +1066,29 @@ def kernel_case(name: str, batch: int, context: int) -> int:
         steps = torch.zeros(batch, dtype=torch.int32, device=device)
         run = lambda i: ops.sample(logits[i % 4], temperature, top_k, top_p, seed, steps)
         work = f"{batch} rows of {vocab} logits, temperature 0.8, top-k 40, top-p 0.9"
+    elif name in ("delta_prefill", "delta_decode"):
+        # the gated delta rule alone: 16 heads of 128 x 128, a prompt of 2048 tokens (prepare,
+        # scan, finish) or `batch` single tokens (one kernel)
+        from mlx_one_b200.parts import FixedState, StateView
+        from mlx_one_b200.parts.mixers import GatedDeltaRule
+
+        sizes = dict(heads=16, kv_heads=8, key_dim=128, value_dim=128, taps=4)
+        slot = GatedDeltaRule.state_size(sizes)
+        channels = 2 * 8 * 128 + 16 * 128
+        wide = channels + 16 * 128 + 2 * 16
+        portions = [PREFILL_TOKENS] if name == "delta_prefill" else [1] * batch
+        ctx, _ = batch_context(portions, [0 if name == "delta_prefill" else context] * len(portions))
+        state = torch.zeros(4 * len(portions), slot, device=device)
+        views = [StateView(state, torch.arange(c * len(portions), (c + 1) * len(portions),
+                                               dtype=torch.int32, device=device),
+                           FixedState((slot,), "float32")) for c in range(4)]
+        rows = [torch.randn(ctx.tokens, wide, device=device).bfloat16() for _ in range(4)]
+        constants = dict(conv=torch.randn(channels, 4, device=device) * 0.5,
+                         a_log=torch.zeros(16, device=device), dt_bias=torch.zeros(16, device=device),
+                         norm_weight=torch.ones(128, device=device), eps=1e-6, unit_eps=1e-6,
+                         ctx=ctx, write=True, **sizes)
+        run = lambda i: ops.gated_delta_rule(rows[i % 4], view=views[i % 4], **constants)
+        work = f"{ctx.tokens} tokens of {len(portions)} requests, 16 heads of 128 x 128, state {slot * 4 / 1e6:.1f} MB a request"
     else:
         print(f"unknown kernel case {name!r}")
         return 2
@@ -1173,7 +1196,7 @@ def main() -> int:
     parser.add_argument("--kernel", default=None,
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
                              "skinny_in_proj, skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
-                             "swapped_swiglu, mixed_attention, sampling, decode_step (the "
+                             "swapped_swiglu, mixed_attention, sampling, delta_prefill, delta_decode, decode_step (the "
                              "whole step, eager, for a launch list), decode_timeline (where "
                              "the graph-replayed step's time goes, kernel by kernel)")
     parser.add_argument("--dependent-launches", type=int, default=1,

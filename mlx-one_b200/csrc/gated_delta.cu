@@ -94,7 +94,6 @@ delta_prepare_kernel(const T* __restrict__ projected, const float* __restrict__ 
                      float* __restrict__ k_out, float* __restrict__ v_out, float* __restrict__ coef,
                      float* __restrict__ kq, DeltaSizes sizes, float unit_eps, int ld) {
     extern __shared__ float mixed[];                 // the token's C channels after conv + silu
-    griddep_launch();
     griddep_wait();
     const int t = blockIdx.x;
     const int r = token_request[t];
@@ -145,6 +144,8 @@ delta_prepare_kernel(const T* __restrict__ projected, const float* __restrict__ 
         coef[((size_t)t * H + h) * 2] = expf(-expf(a_log[h]) * step);
         coef[((size_t)t * H + h) * 2 + 1] = beta;
     }
+    // (the scan's blocks would only wait beside this kernel's if they were let in earlier)
+    griddep_launch();
 }
 
 // ------------------------------------------------------------------ scan
@@ -594,18 +595,11 @@ int launch_delta(const void* projected, const float* conv, const float* a_log, c
                       (const float*)coef, (const float*)kq, (const T*)projected, state, slots,    \
                       request_start, history, o, sizes, write, ld);                               \
     } while (0)
-    // ... and so does 8 lanes when its blocks fill the SMs (156 M instructions, 536 us); with
-    // fewer blocks than half the SMs, 16 lanes make twice as many.
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device);
-    }
-    const bool few = (long long)requests * H * ceil_div_host(V, SCAN_THREADS / 8) * 2 <= sm_count;
+    // ... with 8 lanes 156 M instructions and 536 us. (16 lanes only where a grid of 8-lane blocks
+    // would leave half the SMs empty was measured too, 8 heads: 1112 us against 947 us.)
     if (D <= 32) SCAN(4, 8);
-    else if (D <= 64) { if (few) SCAN(4, 16); else SCAN(8, 8); }
-    else if (D <= 128) { if (few) SCAN(8, 16); else SCAN(16, 8); }
+    else if (D <= 64) SCAN(8, 8);
+    else if (D <= 128) SCAN(16, 8);
     else SCAN(16, 16);
 #undef SCAN
     MLXONE_LAUNCH_CHECK("gated delta rule (scan)");
