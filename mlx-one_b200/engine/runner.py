@@ -10,6 +10,7 @@ mix freely. The reference runs one phase per batch and pads to the widest row
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Any, Sequence
 
@@ -494,6 +495,11 @@ class Runner:
         self.graph_captures += 1
         torch.cuda.current_stream(self.device).synchronize()
         reserved = torch.cuda.memory_reserved(self.device)
+        # No garbage collection while the stream is captured: an object that dies then and gives
+        # pinned or device memory back makes a call that is illegal during a capture, and the
+        # capture is lost ("operation failed due to a previous error during capture").
+        collecting = gc.isenabled()
+        gc.disable()
         try:
             with torch.cuda.graph(graph):
                 result = run()
@@ -505,6 +511,9 @@ class Runner:
             raise RuntimeError(
                 f"a step could not be captured as a CUDA graph ({error}); a part that "
                 "synchronises or reads host values must set `capturable = False`") from error
+        finally:
+            if collecting:
+                gc.enable()
         return graph, result
 
     def _forget_old_portion_graphs(self, newest: tuple) -> None:

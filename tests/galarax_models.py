@@ -71,7 +71,19 @@ G4 = {"architecture": "Galarax", "vocab": 64, "width": 32, "norm": {"eps": 1e-5}
       "layers": [_layer(_left(1, 1, 8, 8, 0.5, {"base": 100.0, "dims": 2}), _right(1, 1, 8, 4, 1), 48)],
       "loop": {"start": 0, "stop": 1, "times": 1}}
 
-CONFIGS = {"G1": (G1, 11, 4), "G2": (G2, 12, 8), "G3": (G3, 13, 16), "G4": (G4, 14, 2)}   # config, seed, page
+# sizes that are multiples of nothing much: width 72, vocabulary 100, three query heads on one key
+# head, keys of 24 and values of 40, six rotated dimensions, five taps, a loop over the last two
+# of three layers, the looped layers of different sizes, one of them without a feed-forward
+G5 = {"architecture": "Galarax", "vocab": 100, "width": 72, "norm": {"eps": 3e-6},
+      "layers": [
+          _layer(_left(3, 1, 24, 40, 0.21, {"base": 5000.0, "dims": 6, "scaling": {
+              "factor": 2.0, "original": 16, "fast": 3.0, "slow": 0.25}}), _right(3, 3, 24, 20, 5), 100),
+          _layer(_left(2, 2, 40, 24, 0.15, {"base": 5000.0, "dims": 40}), _right(4, 1, 12, 36, 3), None),
+          _layer(_left(3, 1, 24, 40, 0.21, None), _right(3, 3, 24, 20, 5), 52)],
+      "loop": {"start": 1, "stop": 3, "times": 2}}
+
+CONFIGS = {"G1": (G1, 11, 4), "G2": (G2, 12, 8), "G3": (G3, 13, 16), "G4": (G4, 14, 2),
+           "G5": (G5, 15, 8)}   # config, seed, page
 
 
 def draw_tensors(config: dict, seed: int, decay_bias: float = 0.0) -> dict[str, torch.Tensor]:
@@ -121,15 +133,22 @@ def make_model_dir(name: str, root: Path | None = None, decay_bias: float = 0.0)
 # mean taken off, relative to the spread of the plain logits. Rounding alone gives 1 to 3 % on
 # these models (measured); a wrong key, a lost state or a token fed twice gives 15 % and more.
 BF16_ROW_ERROR = 0.06
+# A few positions of these random models are badly determined: the plain equations in 32-bit
+# arithmetic land 1e-4 from the 64-bit ones there, a hundred times farther than elsewhere (1e-6),
+# and every rounding of the engine is amplified alike. ``want.noise`` (see PlainModel.logits)
+# measures that per position; a position's bounds grow with it.
+USUAL_NOISE = 5e-6
 
 
 def assert_rows_close(got: torch.Tensor, want: torch.Tensor, dtype, what: str = "") -> None:
-    """float32: every logit within 1e-4 + 1e-4 |plain|. bfloat16: every row's error (see above)
-    within ``BF16_ROW_ERROR``."""
+    """float32: every logit within 1e-4 + 1e-4 |plain| + 4 x the position's noise. bfloat16: every
+    row's error (see above) within ``BF16_ROW_ERROR`` x max(1, noise / USUAL_NOISE)."""
+    noise = getattr(want, "noise", None)
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, f"{what}: {tuple(got.shape)} against {tuple(want.shape)}"
+    noise = torch.zeros(want.shape[0]) if noise is None else noise.float().cpu()
     if dtype == torch.float32:
-        excess = (got - want).abs() - (1e-4 + 1e-4 * want.abs())
+        excess = (got - want).abs() - (1e-4 + 1e-4 * want.abs() + 4 * noise[:, None])
         assert excess.max() <= 0, (f"{what}: logits differ by {(got - want).abs().max():.3e}; rows "
                                    f"{torch.nonzero((excess > 0).any(-1)).flatten().tolist()[:8]}")
         return
@@ -137,5 +156,9 @@ def assert_rows_close(got: torch.Tensor, want: torch.Tensor, dtype, what: str = 
     difference = difference - difference.mean(-1, keepdim=True)
     spread = (want - want.mean(-1, keepdim=True)).pow(2).mean().sqrt()
     rows = difference.pow(2).mean(-1).sqrt() / spread
-    assert rows.max() <= BF16_ROW_ERROR, (f"{what}: row error {rows.max():.3f} of the spread; rows "
-                                          f"{torch.nonzero(rows > BF16_ROW_ERROR).flatten().tolist()[:8]}")
+    allowed = BF16_ROW_ERROR * torch.clamp(noise / USUAL_NOISE, min=1.0)
+    assert (rows <= allowed).all(), (f"{what}: row error {rows.max():.3f} of the spread; rows "
+                                     f"{torch.nonzero(rows > allowed).flatten().tolist()[:8]}")
+    # and most rows are determined well: the looser bound is for the exception
+    assert (noise <= 4 * USUAL_NOISE).float().mean() >= 0.5 or want.shape[0] < 8, \
+        f"{what}: most positions of this request are badly determined; choose other weights"

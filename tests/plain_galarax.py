@@ -199,9 +199,17 @@ class PlainModel:
         self.cfg = json.loads((Path(model_dir) / "config.json").read_text())
         self.w = {name: t.to(kind) for name, t in
                   read_tensors(Path(model_dir) / "model.safetensors").items()}
+        self.w32 = {name: t.to(torch.float32) for name, t in self.w.items()} \
+            if kind == torch.float64 else None
 
     def logits(self, tokens, states=None):
-        return forward(self.cfg, self.w, tokens, states).float()
+        """Logits [T, vocab]. The result carries ``noise`` [T]: how far the same equations in
+        32-bit arithmetic land from the 64-bit ones at each position (largest difference of a
+        logit), a measure of how well the position's logits are determined at all."""
+        out = forward(self.cfg, self.w, tokens, states).float()
+        if self.w32 is not None:
+            out.noise = (forward(self.cfg, self.w32, tokens) - out).abs().amax(dim=-1)
+        return out
 
     def greedy(self, prompt, count):
         tokens = list(prompt)

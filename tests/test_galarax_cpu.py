@@ -148,10 +148,10 @@ def test_stretched_frequencies():
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("galarax")
-    return {name: make_model_dir(name, root) for name in ("G1", "G2", "G4")}
+    return {name: make_model_dir(name, root) for name in ("G1", "G2", "G4", "G5")}
 
 
-@pytest.mark.parametrize("name", ["G1", "G2", "G4"])
+@pytest.mark.parametrize("name", ["G1", "G2", "G4", "G5"])
 def test_whole_and_portions_against_the_plain_model(folders, name):
     config, _, page = CONFIGS[name]
     runner, cache = engine(folders[name], page, 128)

@@ -175,7 +175,8 @@ def delta_pieces(projected, conv, a_log, dt_bias, norm_weight, eps, sizes):
 @pytest.mark.parametrize("sizes", [dict(heads=4, kv_heads=2, key_dim=16, value_dim=24, taps=4),
                                    dict(heads=2, kv_heads=1, key_dim=40, value_dim=8, taps=2),
                                    dict(heads=3, kv_heads=3, key_dim=128, value_dim=40, taps=3),
-                                   dict(heads=1, kv_heads=1, key_dim=200, value_dim=33, taps=1)])
+                                   dict(heads=1, kv_heads=1, key_dim=200, value_dim=33, taps=1),
+                                   dict(heads=2, kv_heads=2, key_dim=24, value_dim=160, taps=5)])
 def test_gated_delta_rule_alone(ops, dtype, sizes):
     """Two requests side by side, each fed in portions of changing size (also single tokens and
     a portion shorter than the convolution), against one pass of the plain recurrence. The
@@ -219,7 +220,8 @@ def test_gated_delta_rule_alone(ops, dtype, sizes):
         want = delta_pieces(projected[r].double(), conv.double(), a_log.double(), dt_bias.double(),
                             norm_weight.double(), eps, sizes)
         difference = (torch.cat(got[r]).double() - want).abs().max()
-        assert difference < bound(dtype, 5e-5, 6e-2), f"request {r}: {difference}"
+        # (bfloat16: the output is rounded to 8 bits of mantissa at values of up to 8)
+        assert difference < bound(dtype, 5e-5, 0.1), f"request {r}: {difference}"
     assert torch.isnan(state[[0, 2, 4]]).all() and torch.isfinite(state[[1, 3]]).all()
 
 
