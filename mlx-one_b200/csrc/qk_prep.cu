@@ -233,33 +233,6 @@ qk_prep_general_kernel(const T* __restrict__ qkv, const float* __restrict__ q_we
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slots_per_token = heads + 2 * kv_heads;
     const int t = blockIdx.x;
-    const int first_slot = warp + WARPS * blockIdx.y, slot_stride = WARPS * gridDim.y;
-    auto source = [&](int slot, int& size) {
-        const bool qk = slot < heads + kv_heads;
-        size = qk ? head_dim : value_dim;
-        return qkv + (size_t)t * ld +
-               (qk ? (size_t)slot * head_dim
-                   : (size_t)(heads + kv_heads) * head_dim +
-                         (size_t)(slot - heads - kv_heads) * value_dim);
-    };
-    // Rows of up to 128 values: the warp's first two heads are asked for at once, before
-    // anything that waits for the token's position or page.
-    constexpr int EARLY = 2, EACH = 4;
-    const bool early = row_dim <= 32 * EACH;
-    float held[EARLY][EACH];
-#pragma unroll
-    for (int s = 0; s < EARLY; ++s) {
-        const int slot = first_slot + s * slot_stride;
-        if (early && slot < slots_per_token) {
-            int size;
-            const T* src = source(slot, size);
-#pragma unroll
-            for (int i = 0; i < EACH; ++i) {
-                const int e = lane + 32 * i;
-                held[s][i] = e < size ? to_float<T>(src[e]) : 0.f;
-            }
-        }
-    }
     const int position = positions[t];
     const int half = rotary_dim / 2;
     if (inv_freq != nullptr) {
@@ -284,26 +257,20 @@ qk_prep_general_kernel(const T* __restrict__ qkv, const float* __restrict__ q_we
         }
     }
     float* values = shared + rotary_dim + warp * row_dim;
-    auto process = [&](int slot, const float* ready) {
+    for (int slot = warp + WARPS * blockIdx.y; slot < slots_per_token; slot += WARPS * gridDim.y) {
         const bool is_q = slot < heads;
         const bool is_k = !is_q && slot < heads + kv_heads;
-        if (!is_q && page_base == nullptr) return;
-        int size;
-        const T* src = source(slot, size);
+        if (!is_q && page_base == nullptr) continue;
+        const int size = (is_q || is_k) ? head_dim : value_dim;
+        const T* src = qkv + (size_t)t * ld +
+                       (is_q || is_k ? (size_t)slot * head_dim
+                                     : (size_t)(heads + kv_heads) * head_dim +
+                                           (size_t)(slot - heads - kv_heads) * value_dim);
         float sum = 0.f;
-        if (ready != nullptr) {
-#pragma unroll
-            for (int i = 0; i < EACH; ++i) {
-                const int e = lane + 32 * i;
-                if (e < row_dim) values[e] = ready[i];
-                sum += e < row_dim ? ready[i] * ready[i] : 0.f;
-            }
-        } else {
-            for (int e = lane; e < row_dim; e += 32) {
-                const float v = e < size ? to_float<T>(src[e]) : 0.f;
-                values[e] = v;
-                sum += v * v;
-            }
+        for (int e = lane; e < row_dim; e += 32) {
+            const float v = e < size ? to_float<T>(src[e]) : 0.f;
+            values[e] = v;
+            sum += v * v;
         }
         if (is_q || is_k) {
             const float* weight = is_q ? q_weight : k_weight;
@@ -342,12 +309,7 @@ qk_prep_general_kernel(const T* __restrict__ qkv, const float* __restrict__ q_we
         }
         for (int e = lane; e < row_dim; e += 32) dst[e] = from_float<T>(values[e]);
         __syncwarp();
-    };
-    if (first_slot < slots_per_token) process(first_slot, early ? held[0] : nullptr);
-    if (first_slot + slot_stride < slots_per_token)
-        process(first_slot + slot_stride, early ? held[1] : nullptr);
-    for (int slot = first_slot + EARLY * slot_stride; slot < slots_per_token; slot += slot_stride)
-        process(slot, nullptr);
+    }
 }
 
 template <int HD>
