@@ -207,3 +207,23 @@ def test_greedy_generation_through_the_entry_point(folders):
     for prompt, result in zip(batch, results):
         assert list(result.token_ids) == plain.greedy(prompt, 6)
     engine_.close()
+
+
+def test_command_line_writes_a_random_model(tmp_path):
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from plain_galarax import read_tensors
+
+    root = Path(__file__).resolve().parent.parent
+    (tmp_path / "config.json").write_text(json.dumps(G1))
+    done = subprocess.run([sys.executable, str(root / "bin" / "mlx-one"), "random-model",
+                           str(tmp_path / "config.json"), str(tmp_path / "model"), "--seed", "3"],
+                          capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr
+    stored = read_tensors(tmp_path / "model" / "model.safetensors")
+    assert stored["l2.mix.right.v.conv"].shape == (16, 2) and stored["loop.step"].shape == (2, 64)
+    assert json.loads((tmp_path / "model" / "config.json").read_text())["architecture"] == "Galarax"
+    # norm weights stored around zero, plain weights around one
+    assert stored["l0.norm1"].float().abs().mean() < 0.3 < stored["l0.mix.left.out"].float().mean()

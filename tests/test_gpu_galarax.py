@@ -382,3 +382,52 @@ def test_greedy_generation_through_the_entry_point(folders, plain):
     for prompt, result in zip(batch, results):
         assert list(result.token_ids) == plain["G1"].greedy(prompt, 12)
     engine_.close()
+
+
+def test_command_line_and_trace_replay(folders, plain, tmp_path):
+    """`mlx-one generate` with token ids (greedy against the plain model, sampled with a seed) and
+    `trace_run` as a process: steps on standard input, logits files out, requests ended and their
+    slots used again."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    root = Path(__file__).resolve().parent.parent
+    folder = folders["G2"]
+    run = lambda *args: subprocess.run([sys.executable, str(root / "bin" / "mlx-one"), *args],
+                                       capture_output=True, text=True, timeout=600)
+    greedy = run("generate", str(folder), "5 17 3 200", "--token-ids", "--max-tokens", "6",
+                 "--dtype", "float32")
+    assert greedy.returncode == 0, greedy.stderr
+    assert [int(t) for t in greedy.stdout.split()] == plain["G2"].greedy([5, 17, 3, 200], 6)
+    sampled = [run("generate", str(folder), "5 17 3", "--token-ids", "--max-tokens", "8",
+                   "--temperature", "0.9", "--top-k", "30", "--seed", "11") for _ in range(2)]
+    assert sampled[0].returncode == 0 and sampled[0].stdout == sampled[1].stdout
+    assert len(sampled[0].stdout.split()) == 8
+
+    vocab = CONFIGS["G2"][0]["vocab"]
+    a, b, c = prompts(vocab, (21, 9, 30), seed=17)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:8], "want": [0, 7]},
+                                     {"id": "b", "tokens": b, "want": [8]}], "end": ["b"]},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[8:20], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[20:], "want": [0]},
+                                     {"id": "c", "tokens": c[:2], "want": [1]}], "end": ["a"]},
+             {"step": 3, "entries": [{"id": "c", "tokens": c[2:], "want": [27]}], "end": ["c"]}]
+    out = tmp_path / "logits"
+    done = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder),
+                           "--dtype", "float32", "--out", str(out), "--max-tokens", "128",
+                           "--max-requests", "2"],
+                          input="".join(json.dumps(step) + "\n" for step in steps),
+                          capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr
+    assert [line for line in done.stdout.split("\n") if line.startswith("done")] == \
+        [f"done {i}" for i in range(4)]
+    read = lambda step, rows: torch.from_numpy(np.fromfile(out / f"{step}.f32", dtype="<f4")).view(rows, vocab)
+    assert not (out / "1.f32").exists()
+    wa, wb, wc = (plain["G2"].logits(t) for t in (a, b, c))
+    assert_close(read(0, 3), torch.stack([wa[0], wa[7], wb[8]]), torch.float32, "step 0")
+    assert_close(read(2, 2), torch.stack([wa[20], wc[1]]), torch.float32, "step 2")
+    assert_close(read(3, 1), wc[29:30], torch.float32, "step 3")
