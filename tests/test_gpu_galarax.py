@@ -121,14 +121,15 @@ def test_rotation_norm_and_page_write(ops, dtype, dim, vdim, dims, amplitude_fac
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dim, vdim", [(32, 16), (96, 80), (72, 112), (128, 128), (24, 200)])
 @pytest.mark.parametrize("portion", [1, 37])
-def test_a_far_key_stands_out(ops, dtype, portion):
+def test_a_far_key_stands_out(ops, dtype, portion, dim, vdim):
     """One key hundreds of positions back (just after a page border) is the only one that matches
     the last queries: their output must be that key's value. Decoded alone and in a portion."""
     from mlx_one_b200.parts import PagedKeyValues, PagedView
 
-    heads, kv_heads, dim, vdim, page, eps, scale = 2, 1, 32, 16, 16, 1e-6, 1.0
-    total, far = 600, 33
+    heads, kv_heads, page, eps, scale = 2, 1, 16, 1e-6, 32.0 / dim
+    total, far, row = 600, 33, max(dim, vdim)
     generator = torch.Generator().manual_seed(5)
     q = torch.randn(total, heads, dim, generator=generator)
     k = torch.randn(total, kv_heads, dim, generator=generator)
@@ -141,8 +142,8 @@ def test_a_far_key_stands_out(ops, dtype, portion):
     assert (want[-1, 0] - qkv[far, (heads + 1) * dim:].double()).abs().max() < 0.05
     blocks = math.ceil(total / page)
     table = torch.arange(blocks, dtype=torch.int32).flip(0)[None].contiguous().to(DEVICE)
-    kv = torch.zeros(2, blocks + 1, kv_heads, page, dim, dtype=dtype, device=DEVICE)
-    view = PagedView(kv, table, page, PagedKeyValues(kv_heads, dim, None))
+    kv = torch.zeros(2, blocks + 1, kv_heads, page, row, dtype=dtype, device=DEVICE)
+    view = PagedView(kv, table, page, PagedKeyValues(kv_heads, row, None))
     common = dict(heads=heads, kv_heads=kv_heads, head_dim=dim, q_weight=None, k_weight=None, eps=eps,
                   rotary=None, scale=scale, window=None, view=view, write=True, value_dim=vdim,
                   amplitude=1.0, norm_after=True)
@@ -150,7 +151,8 @@ def test_a_far_key_stands_out(ops, dtype, portion):
     ops.qkv_attention(qkv[:first].to(DEVICE), ctx=context([first], [0]), **common)
     got = ops.qkv_attention(qkv[first:].to(DEVICE), ctx=context([portion], [first]), **common)
     ops.check_errors()
-    got = got.view(portion, heads, dim)[..., :vdim].cpu().double()
+    assert (got.view(portion, heads, row)[..., vdim:] == 0).all()
+    got = got.view(portion, heads, row)[..., :vdim].cpu().double()
     assert (got - want[first:]).abs().max() < bound(dtype, 1e-4, 3e-2)
 
 
