@@ -30,6 +30,7 @@ class Architecture:
 _BUILTIN = {
     "lfm2": "mlx_one_b200.architectures.lfm2:ARCHITECTURE",
     "galarax": "mlx_one_b200.architectures.galarax:ARCHITECTURE",
+    "farorax": "mlx_one_b200.architectures.farorax:ARCHITECTURE",
 }
 _REGISTERED: dict[str, Architecture] = {}
 

@@ -5,7 +5,8 @@
 // been written there before). Keys are taken 32 at a time, in blocks aligned to absolute
 // positions, one key per lane; softmax statistics and the output are kept in 32-bit and
 // updated block by block (online softmax). The order of operations for a query depends only
-// on its position, never on how the tokens were cut into steps or batched.
+// on its position, never on how the tokens were cut into steps or batched. `sinks` (float32
+// [heads] or null) adds exp(sink) of the query's head to the softmax's denominator.
 //
 // This kernel serves the 32-bit engine and every shape that the faster kernels refuse.
 #include "common.cuh"
@@ -23,7 +24,7 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv,
                          long long kv_half, const int* __restrict__ positions,
                          const int* __restrict__ token_request, T* __restrict__ out, int tokens,
                          int heads, int kv_heads, int head_dim, float scale, int window,
-                         int* __restrict__ error_flag) {
+                         const float* __restrict__ sinks, int* __restrict__ error_flag) {
     extern __shared__ float shared[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -41,7 +42,10 @@ attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kv,
     __syncwarp();
 
     const int lowest = window > 0 ? max(position - window + 1, 0) : 0;
+    // A sink is a term exp(sink) of the denominator that has no key and no value: the softmax
+    // starts from it (maximum = sink, sum = 1, output = 0) instead of from nothing.
     float running_max = -INFINITY, running_sum = 0.f;
+    if (sinks != nullptr) { running_max = sinks[head]; running_sum = 1.f; }
     float acc[MAX_ACC];
 #pragma unroll
     for (int i = 0; i < MAX_ACC; ++i) acc[i] = 0.f;
@@ -104,8 +108,8 @@ MLXONE_API int mlxone_attention_generic(const void* q, const void* kv, const int
                                         int table_width, int page_size, int pages,
                                         const int* positions, const int* token_request, void* out,
                                         int tokens, int heads, int kv_heads, int head_dim,
-                                        float scale, int window, int dtype, int* error_flag,
-                                        cudaStream_t stream) {
+                                        float scale, int window, int dtype, const float* sinks,
+                                        int* error_flag, cudaStream_t stream) {
     if (tokens == 0) return 0;
     MLXONE_REQUIRE(tokens > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
                    "attention: %d heads cannot share %d key heads", heads, kv_heads);
@@ -120,12 +124,14 @@ MLXONE_API int mlxone_attention_generic(const void* q, const void* kv, const int
         using T = __nv_bfloat16;
         attention_generic_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
             (const T*)q, (const T*)kv, block_table, table_width, page_size, kv_half, positions,
-            token_request, (T*)out, tokens, heads, kv_heads, head_dim, scale, window, error_flag);
+            token_request, (T*)out, tokens, heads, kv_heads, head_dim, scale, window, sinks,
+            error_flag);
     } else {
         using T = float;
         attention_generic_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
             (const T*)q, (const T*)kv, block_table, table_width, page_size, kv_half, positions,
-            token_request, (T*)out, tokens, heads, kv_heads, head_dim, scale, window, error_flag);
+            token_request, (T*)out, tokens, heads, kv_heads, head_dim, scale, window, sinks,
+            error_flag);
     }
     MLXONE_LAUNCH_CHECK("attention_generic");
     return 0;

@@ -251,7 +251,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                          const int* __restrict__ block_table, int table_width, int page_size,
                          const int* __restrict__ request_start, const int* __restrict__ history,
                          bf16* __restrict__ out, int requests, int heads, int kv_heads,
-                         float scale_log2, int window) {
+                         float scale_log2, int window, const float* __restrict__ sinks) {
     using T = Tile<HD>;
     constexpr int KEYS = PREFILL_KEYS;
     extern __shared__ __align__(16) unsigned char shared_bytes[];
@@ -314,6 +314,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
         limit_lo[i] = window > 0 ? max(position - window + 1, 0) : 0;
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (sinks != nullptr) {
+        // a sink is a term exp(sink) of the denominator without a key or a value: the softmax
+        // starts from it (maximum in units of log2, sum 1, output 0)
+        m[0] = m[1] = sinks[head] * LOG2E;
+        l[0] = l[1] = 1.f;
+    }
     float o[HD / 8][4];
 #pragma unroll
     for (int n = 0; n < HD / 8; ++n)
@@ -426,7 +432,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
                         const int* __restrict__ block_table, int table_width, int page_size,
                         const int* __restrict__ positions, bf16* __restrict__ out,
                         float* __restrict__ partial, int heads, int kv_heads, int splits,
-                        float scale_log2, int window, DecodePrep prep) {
+                        float scale_log2, int window, DecodePrep prep,
+                        const float* __restrict__ sinks) {
     using T = Tile<HD>;
     constexpr int KEYS = DECODE_KEYS;
     constexpr int ROW_FLOATS = HD + 2;
@@ -607,6 +614,17 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     }
     const bool head_live[2] = {2 * t < rows, 2 * t + 1 < rows};
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};      // per head 2t, 2t + 1
+    if (sinks != nullptr && split == 0 && warp == 0) {
+        // a sink (a term exp(sink) of the denominator without key or value) is where the first
+        // warp of the first split starts from: maximum in units of log2, sum 1 (held by one of
+        // the lanes whose shares are added at the end), output 0
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            if (head_live[i]) {
+                m[i] = sinks[head0 + 2 * t + i] * LOG2E;
+                if (g == 0) l[i] = 1.f;
+            }
+    }
     float o[HD / 16][4];
 #pragma unroll
     for (int d = 0; d < HD / 16; ++d)
@@ -892,7 +910,7 @@ template <int HD>
 int launch_prefill(const void* q, const void* kv, long long kv_half, const int* block_table,
                    int table_width, int page_size, const int* request_start, const int* history,
                    void* out, int tokens, int requests, int heads, int kv_heads, float scale,
-                   int window, cudaStream_t stream) {
+                   int window, const float* sinks, cudaStream_t stream) {
     using T = Tile<HD>;
     const size_t shared = (size_t)(ROWS + 4 * PREFILL_KEYS) * T::STRIDE * 2;
     auto kernel = attention_prefill_kernel<HD>;
@@ -901,7 +919,8 @@ int launch_prefill(const void* q, const void* kv, long long kv_half, const int* 
     const dim3 grid((tokens + ROWS - 1) / ROWS + requests, heads);
     kernel<<<grid, PREFILL_WARPS * 32, shared, stream>>>(
         (const bf16*)q, (const bf16*)kv, kv_half, block_table, table_width, page_size,
-        request_start, history, (bf16*)out, requests, heads, kv_heads, scale * LOG2E, window);
+        request_start, history, (bf16*)out, requests, heads, kv_heads, scale * LOG2E, window,
+        sinks);
     return 0;
 }
 
@@ -915,7 +934,7 @@ template <int HD, bool PREP>
 int launch_decode(const void* q, const void* kv, long long kv_half, const int* block_table,
                   int table_width, int page_size, const int* positions, void* out, float* partial,
                   int requests, int heads, int kv_heads, int splits, float scale, int window,
-                  cudaStream_t stream, DecodePrep prep = DecodePrep()) {
+                  const float* sinks, cudaStream_t stream, DecodePrep prep = DecodePrep()) {
     using T = Tile<HD>;
     const size_t shared = decode_shared_bytes(HD);
     const int group = heads / kv_heads;
@@ -943,7 +962,7 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
         const cudaError_t err = cudaLaunchKernelEx(
             &config, kernel, (const bf16*)q, (const bf16*)kv, kv_half, block_table, table_width,
             page_size, positions, (bf16*)out, (float*)nullptr, heads, kv_heads, splits, scale_log2,
-            window, prep);
+            window, prep, sinks);
         if (err != cudaSuccess) {
             mlxone_set_error("attention_decode: cluster launch failed: %s", cudaGetErrorString(err));
             return 2;
@@ -955,7 +974,7 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     launch_kernel(kernel, grid, dim3(DECODE_WARPS * 32), shared, stream, true, (const bf16*)q,
                   (const bf16*)kv, kv_half, block_table, table_width, page_size, positions,
-                  (bf16*)out, partial, heads, kv_heads, splits, scale_log2, window, prep);
+                  (bf16*)out, partial, heads, kv_heads, splits, scale_log2, window, prep, sinks);
     if (splits > 1) {
         const int items = requests * heads;
         launch_kernel(attention_merge_kernel<HD>, dim3((items + 3) / 4), dim3(128), 0, stream, true,
@@ -1002,7 +1021,7 @@ MLXONE_API int mlxone_attention_prefill(const void* q, const void* kv, const int
                                         int table_width, int page_size, int pages,
                                         const int* request_start, const int* history, void* out,
                                         int tokens, int requests, int heads, int kv_heads,
-                                        int head_dim, float scale, int window,
+                                        int head_dim, float scale, int window, const float* sinks,
                                         cudaStream_t stream) {
     if (tokens == 0) return 0;
     MLXONE_REQUIRE(tokens > 0 && requests > 0 && heads > 0 && kv_heads > 0 &&
@@ -1013,7 +1032,7 @@ MLXONE_API int mlxone_attention_prefill(const void* q, const void* kv, const int
     const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
 #define CALL(HD)                                                                              \
     launch_prefill<HD>(q, kv, kv_half, block_table, table_width, page_size, request_start,    \
-                       history, out, tokens, requests, heads, kv_heads, scale, window, stream)
+                       history, out, tokens, requests, heads, kv_heads, scale, window, sinks, stream)
     MLXONE_HEAD_DIMS(CALL)
 #undef CALL
     MLXONE_LAUNCH_CHECK("attention_prefill");
@@ -1026,11 +1045,14 @@ MLXONE_API long long mlxone_attention_decode_scratch(int requests, int heads, in
     return splits > 1 ? (long long)requests * heads * splits * (head_dim + 2) : 0;
 }
 
-MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int* block_table,
-                                       int table_width, int page_size, int pages,
-                                       const int* positions, void* out, float* partial,
-                                       int requests, int heads, int kv_heads, int head_dim,
-                                       int splits, float scale, int window, cudaStream_t stream) {
+// `sinks` (float32 [heads] or null): exp(sink) of a query's head stands in the denominator of
+// its softmax, beside the keys' terms.
+MLXONE_API int mlxone_attention_decode_sinks(const void* q, const void* kv, const int* block_table,
+                                             int table_width, int page_size, int pages,
+                                             const int* positions, void* out, float* partial,
+                                             int requests, int heads, int kv_heads, int head_dim,
+                                             int splits, float scale, int window,
+                                             const float* sinks, cudaStream_t stream) {
     if (requests == 0) return 0;
     MLXONE_REQUIRE(requests > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
                    "attention_decode: bad sizes");
@@ -1043,11 +1065,21 @@ MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int*
     const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
 #define CALL(HD)                                                                               \
     launch_decode<HD, false>(q, kv, kv_half, block_table, table_width, page_size, positions, out, \
-                             partial, requests, heads, kv_heads, splits, scale, window, stream)
+                             partial, requests, heads, kv_heads, splits, scale, window, sinks, stream)
     MLXONE_HEAD_DIMS(CALL)
 #undef CALL
     MLXONE_LAUNCH_CHECK("attention_decode");
     return 0;
+}
+
+MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int* block_table,
+                                       int table_width, int page_size, int pages,
+                                       const int* positions, void* out, float* partial,
+                                       int requests, int heads, int kv_heads, int head_dim,
+                                       int splits, float scale, int window, cudaStream_t stream) {
+    return mlxone_attention_decode_sinks(q, kv, block_table, table_width, page_size, pages,
+                                         positions, out, partial, requests, heads, kv_heads,
+                                         head_dim, splits, scale, window, nullptr, stream);
 }
 
 // The merge of key splits alone: partial [items, splits, head_dim + 2] (unnormalised output,
@@ -1083,8 +1115,8 @@ MLXONE_API int mlxone_attention_decode_fused(const void* qkv, const float* q_wei
                                              int page_size, int pages, const int* positions,
                                              void* out, float* partial, int requests, int heads,
                                              int kv_heads, int head_dim, int splits, float scale,
-                                             int window, int write_kv, int* error_flag,
-                                             cudaStream_t stream) {
+                                             int window, int write_kv, const float* sinks,
+                                             int* error_flag, cudaStream_t stream) {
     if (requests == 0) return 0;
     MLXONE_REQUIRE(mlxone_attention_decode_fused_supports(head_dim),
                    "attention_decode_fused: head size %d is no multiple of 32 up to 128", head_dim);
@@ -1106,7 +1138,7 @@ MLXONE_API int mlxone_attention_decode_fused(const void* qkv, const float* q_wei
         case HD:                                                                                  \
             code = launch_decode<HD, true>(qkv, kv, kv_half, block_table, table_width, page_size, \
                                            positions, out, partial, requests, heads, kv_heads,    \
-                                           splits, scale, window, stream, prep);                  \
+                                           splits, scale, window, sinks, stream, prep);           \
             break;
         CASE(32) CASE(64) CASE(96) CASE(128)
 #undef CASE

@@ -54,12 +54,12 @@ MLXONE_API int mlxone_embedding(const int* ids, const void* table, float* out, i
 }
 
 // ------------------------------------------------------------------ add + RMSNorm
-// residual[t, :] += delta[t, :] (if delta); out[t, :] = residual * rsqrt(mean(residual^2)
+// residual[t, :] += delta_scale * delta[t, :] (if delta); out[t, :] = residual * rsqrt(mean(residual^2)
 // + eps) * weight. One block per row; sums in 32-bit in an order fixed by the row length.
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const float* __restrict__ weight, T* __restrict__ out,
-                                   int hidden, float eps) {
+                                   int hidden, float eps, float delta_scale) {
     __shared__ float scratch[33];
     griddep_launch();
     griddep_wait();
@@ -68,7 +68,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float v = residual[base + c];
         if (delta != nullptr) {
-            v += to_float<T>(delta[base + c]);
+            v = fmaf(delta_scale, to_float<T>(delta[base + c]), v);
             residual[base + c] = v;
         }
         sum += v * v;
@@ -112,7 +112,7 @@ template <> struct Vec4<__nv_bfloat16> {
 template <typename T, int PASSES>
 __global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                         const float* __restrict__ weight, T* __restrict__ out,
-                                        int hidden, float eps) {
+                                        int hidden, float eps, float delta_scale) {
     __shared__ float scratch[33];
     griddep_launch();
     // the norm's weights do not depend on the kernel before this one: they are on their way
@@ -140,7 +140,7 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const T* _
                 float more[4];
                 Vec4<T>::load(delta + base + c, more);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) values[pass][i] += more[i];
+                for (int i = 0; i < 4; ++i) values[pass][i] = fmaf(delta_scale, more[i], values[pass][i]);
                 Vec4<float>::store(residual + base + c, values[pass]);
             }
 #pragma unroll
@@ -167,7 +167,7 @@ template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_warp_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                         const float* __restrict__ weight, T* __restrict__ out, int rows,
-                        int hidden, float eps) {
+                        int hidden, float eps, float delta_scale) {
     griddep_launch();
     griddep_wait();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -191,7 +191,7 @@ add_rmsnorm_warp_kernel(float* __restrict__ residual, const T* __restrict__ delt
                 float more[4];
                 Vec4<T>::load(delta + base + c, more);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) values[j][i] += more[i];
+                for (int i = 0; i < 4; ++i) values[j][i] = fmaf(delta_scale, more[i], values[j][i]);
                 Vec4<float>::store(residual + base + c, values[j]);
             }
         }
@@ -217,7 +217,7 @@ add_rmsnorm_warp_kernel(float* __restrict__ residual, const T* __restrict__ delt
 
 template <typename T>
 static cudaError_t launch_add_rmsnorm(float* residual, const void* delta, const float* weight,
-                                      void* out, int rows, int hidden, float eps,
+                                      void* out, int rows, int hidden, float eps, float delta_scale,
                                       cudaStream_t stream) {
     const bool aligned = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(residual) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
@@ -229,12 +229,12 @@ static cudaError_t launch_add_rmsnorm(float* residual, const void* delta, const 
         const dim3 grid((rows + 7) / 8);
         if (hidden <= 512)
             return launch_kernel(add_rmsnorm_warp_kernel<T, 4>, grid, dim3(256), 0, stream, true,
-                                 residual, (const T*)delta, weight, (T*)out, rows, hidden, eps);
+                                 residual, (const T*)delta, weight, (T*)out, rows, hidden, eps, delta_scale);
         if (hidden <= 1024)
             return launch_kernel(add_rmsnorm_warp_kernel<T, 8>, grid, dim3(256), 0, stream, true,
-                                 residual, (const T*)delta, weight, (T*)out, rows, hidden, eps);
+                                 residual, (const T*)delta, weight, (T*)out, rows, hidden, eps, delta_scale);
         return launch_kernel(add_rmsnorm_warp_kernel<T, 16>, grid, dim3(256), 0, stream, true,
-                             residual, (const T*)delta, weight, (T*)out, rows, hidden, eps);
+                             residual, (const T*)delta, weight, (T*)out, rows, hidden, eps, delta_scale);
     }
     if (aligned && hidden <= 8192) {
         const int quads = hidden / 4;
@@ -242,24 +242,25 @@ static cudaError_t launch_add_rmsnorm(float* residual, const void* delta, const 
         int threads = ((quads + passes - 1) / passes + 31) / 32 * 32;
         if (passes == 1)
             return launch_kernel(add_rmsnorm_rows_kernel<T, 1>, dim3(rows), dim3(threads), 0, stream,
-                                 true, residual, (const T*)delta, weight, (T*)out, hidden, eps);
+                                 true, residual, (const T*)delta, weight, (T*)out, hidden, eps, delta_scale);
         return launch_kernel(add_rmsnorm_rows_kernel<T, 2>, dim3(rows), dim3(threads), 0, stream,
-                             true, residual, (const T*)delta, weight, (T*)out, hidden, eps);
+                             true, residual, (const T*)delta, weight, (T*)out, hidden, eps, delta_scale);
     }
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     return launch_kernel(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, stream, true, residual,
-                         (const T*)delta, weight, (T*)out, hidden, eps);
+                         (const T*)delta, weight, (T*)out, hidden, eps, delta_scale);
 }
 
 MLXONE_API int mlxone_add_rmsnorm(float* residual, const void* delta, const float* weight,
                                   void* out, int rows, int hidden, float eps, int dtype,
-                                  cudaStream_t stream) {
+                                  float delta_scale, cudaStream_t stream) {
     if (rows == 0) return 0;
     MLXONE_REQUIRE(rows > 0 && hidden > 0, "add_rmsnorm: bad sizes");
     if (dtype == MLXONE_BF16)
-        launch_add_rmsnorm<__nv_bfloat16>(residual, delta, weight, out, rows, hidden, eps, stream);
+        launch_add_rmsnorm<__nv_bfloat16>(residual, delta, weight, out, rows, hidden, eps, delta_scale,
+                                          stream);
     else
-        launch_add_rmsnorm<float>(residual, delta, weight, out, rows, hidden, eps, stream);
+        launch_add_rmsnorm<float>(residual, delta, weight, out, rows, hidden, eps, delta_scale, stream);
     MLXONE_LAUNCH_CHECK("add_rmsnorm");
     return 0;
 }

@@ -32,6 +32,8 @@
 // three projections nor a second kernel touch memory).
 #include "common.cuh"
 
+#include <cstring>
+
 namespace {
 
 using bf16 = __nv_bfloat16;
@@ -46,6 +48,7 @@ enum : int { STORE_BF16 = 0, SWIGLU = 1, ADD_RESIDUAL = 2, STORE_F32 = 3, GATED_
              ACTIVATE = 5 };   // ACTIVATE: bf16 store of an activation (its code rides in up_offset)
 // epilogue codes of the C interface from this on mean ACTIVATE with activation (code - this)
 constexpr int ACTIVATE_BASE = 16;
+constexpr int ONE_BITS = 0x3f800000;      // 1.0f
 
 // What the gated-convolution epilogue needs beside the product: one token per request.
 struct ConvUpdate {
@@ -619,7 +622,9 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
             } else if (EPILOGUE == ADD_RESIDUAL) {
                 // added where the value lives (one addition per address, so the result is the
                 // same): the thread does not wait for the old value to come and go
-                atomicAdd(reinterpret_cast<float*>(out) + (size_t)token * ldo + column, value);
+                // (the factor on what is added rides in up_offset as a float's bits)
+                atomicAdd(reinterpret_cast<float*>(out) + (size_t)token * ldo + column,
+                          value * __int_as_float(up_offset));
             } else {
                 reinterpret_cast<float*>(out)[(size_t)token * ldo + column] = value;
             }
@@ -716,7 +721,31 @@ cudaError_t launch_for_rows(const void* a, int lda, const void* w, const float* 
 }  // namespace
 
 // Most rows (tokens) that the skinny product takes; more go to the library product.
+// (ONE_BITS, the bits of 1.0f: the factor of an ordinary addition into the residual.)
 MLXONE_API int mlxone_gemm_skinny_max_rows() { return 32; }
+
+// out[m, n] (the float32 residual) += scale * (a w^T + bias).
+MLXONE_API int mlxone_gemm_skinny_scaled_add(const void* a, int lda, const void* w,
+                                             const float* bias, void* out, int ldo, int m, int n,
+                                             int k, float scale, cudaStream_t stream) {
+    if (m == 0 || n == 0) return 0;
+    MLXONE_REQUIRE(m > 0 && m <= 32, "gemm_skinny: %d rows, at most 32", m);
+    MLXONE_REQUIRE(n > 0 && k > 0 && k % 8 == 0 && lda % 8 == 0,
+                   "gemm_skinny: K (%d) and the row stride of a (%d) must be multiples of 8", k, lda);
+    MLXONE_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                   "gemm_skinny: operands must be 16-byte aligned");
+    int bits;
+    memcpy(&bits, &scale, sizeof(bits));
+    const cudaError_t err = launch_for_rows<ADD_RESIDUAL>(a, lda, w, bias, out, ldo, m, n, k, bits,
+                                                          stream);
+    if (err != cudaSuccess) {
+        mlxone_set_error("gemm_skinny: launch failed: %s", cudaGetErrorString(err));
+        return 2;
+    }
+    MLXONE_LAUNCH_CHECK("gemm_skinny");
+    return 0;
+}
 
 // epilogue: 0 = out bf16 [m, n]; 1 = SwiGLU, w is [gate rows; up rows] with n = 2 * width, out
 // bf16 [m, width]; 2 = out is the float32 residual [m, n], added in place; 3 = out float32;
@@ -746,7 +775,7 @@ MLXONE_API int mlxone_gemm_skinny(const void* a, int lda, const void* w, const f
         case SWIGLU:
             err = launch_for_rows<SWIGLU>(a, lda, w, bias, out, ldo, m, n, k, n / 2, stream); break;
         case ADD_RESIDUAL:
-            err = launch_for_rows<ADD_RESIDUAL>(a, lda, w, bias, out, ldo, m, n, k, 0, stream); break;
+            err = launch_for_rows<ADD_RESIDUAL>(a, lda, w, bias, out, ldo, m, n, k, ONE_BITS, stream); break;
         default:
             err = launch_for_rows<STORE_F32>(a, lda, w, bias, out, ldo, m, n, k, 0, stream); break;
     }
@@ -870,7 +899,7 @@ MLXONE_API int mlxone_gemm_skinny_norm(const float* source, int source_ld,
         case SWIGLU:
             err = launch_for_rows<SWIGLU>(nullptr, 0, w, bias, out, ldo, m, n, k, n / 2, stream, norm); break;
         case ADD_RESIDUAL:
-            err = launch_for_rows<ADD_RESIDUAL>(nullptr, 0, w, bias, out, ldo, m, n, k, 0, stream, norm); break;
+            err = launch_for_rows<ADD_RESIDUAL>(nullptr, 0, w, bias, out, ldo, m, n, k, ONE_BITS, stream, norm); break;
         default:
             err = launch_for_rows<STORE_F32>(nullptr, 0, w, bias, out, ldo, m, n, k, 0, stream, norm); break;
     }

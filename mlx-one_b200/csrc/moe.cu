@@ -1,0 +1,152 @@
+// Routing of a mixture of experts, and the routing weights multiplied into the experts' columns
+// of a stacked activation.
+//
+// Per token: logits z = W_r x in 32-bit (x may be in the compute dtype), scores s = sigmoid(z).
+// The experts form `groups` equal runs of neighbours; a group's score is the sum of its
+// `group_score` largest scores, and only experts of the `keep` best groups may be chosen. The
+// `top` allowed experts with the largest scores are chosen (ties: the lower index) and weighted
+// with s / (sum of the chosen s + 1e-20); all others get weight 0.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_EXPERTS = 512;
+constexpr int ROUTE_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_experts_kernel(const T* __restrict__ x, int ld, const float* __restrict__ router,
+                     float* __restrict__ weights, int hidden, int experts, int top, int groups,
+                     int keep, int group_score) {
+    __shared__ float score[MAX_EXPERTS];
+    __shared__ float group_value[MAX_EXPERTS];
+    __shared__ unsigned char allowed[MAX_EXPERTS];
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* row = x + (size_t)t * ld;
+    for (int e = threadIdx.x; e < experts; e += ROUTE_THREADS) allowed[e] = 0;
+    // a warp per expert in turn; the lanes' partial sums are added in a fixed order
+    for (int e = warp; e < experts; e += ROUTE_THREADS / 32) {
+        const float* w = router + (size_t)e * hidden;
+        float sum = 0.f;
+        for (int c = lane; c < hidden; c += 32) sum = fmaf(to_float<T>(row[c]), w[c], sum);
+        sum = warp_sum(sum);
+        if (lane == 0) score[e] = 1.f / (1.f + expf(-sum));
+    }
+    __syncthreads();
+    const int per = experts / groups;
+    // a group's score: the sum of its largest `group_score` scores (one thread per group)
+    for (int g = threadIdx.x; g < groups; g += ROUTE_THREADS) {
+        float total = 0.f;
+        unsigned long long taken_lo = 0ull;       // groups of up to 64 experts keep a mask;
+        for (int pick = 0; pick < min(group_score, per); ++pick) {
+            int best = -1;
+            float best_value = -1.f;
+            for (int i = 0; i < per; ++i) {
+                const bool taken = per <= 64 ? ((taken_lo >> i) & 1ull) != 0ull
+                                             : allowed[g * per + i] == 2;
+                if (!taken && score[g * per + i] > best_value) { best_value = score[g * per + i]; best = i; }
+            }
+            if (best < 0) break;
+            total += best_value;
+            if (per <= 64) taken_lo |= 1ull << best; else allowed[g * per + best] = 2;
+        }
+        group_value[g] = total;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // the `keep` best groups (ties: the lower index), then the `top` best allowed experts
+        for (int e = 0; e < experts; ++e) allowed[e] = 0;
+        for (int pick = 0; pick < keep; ++pick) {
+            int best = -1;
+            float best_value = -1.f;
+            for (int g = 0; g < groups; ++g)
+                if (group_value[g] > best_value) { best_value = group_value[g]; best = g; }
+            if (best < 0) break;
+            group_value[best] = -2.f;
+            for (int i = 0; i < per; ++i) allowed[best * per + i] = 1;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += ROUTE_THREADS)
+        weights[(size_t)t * experts + e] = 0.f;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.f;
+        int chosen[64];
+        int count = 0;
+        for (int pick = 0; pick < top && pick < 64; ++pick) {
+            int best = -1;
+            float best_value = -1.f;
+            for (int e = 0; e < experts; ++e)
+                if (allowed[e] == 1 && score[e] > best_value) { best_value = score[e]; best = e; }
+            if (best < 0) break;
+            allowed[best] = 3;
+            chosen[count++] = best;
+            total += best_value;
+        }
+        const float inverse = 1.f / (total + 1e-20f);
+        for (int i = 0; i < count; ++i)
+            weights[(size_t)t * experts + chosen[i]] = score[chosen[i]] * inverse;
+    }
+}
+
+// x[t, e * width + f] *= weights[t, e] for e < experts (columns beyond experts * width stay).
+template <typename T>
+__global__ void scale_expert_columns_kernel(T* __restrict__ x, int ld, const float* __restrict__ weights,
+                                            int experts, int width, long long total) {
+    griddep_launch();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int across = experts * width;
+    const long long t = i / across;
+    const int c = (int)(i - t * across);
+    const float w = weights[t * experts + c / width];
+    T* at = x + t * ld + c;
+    *at = from_float<T>(to_float<T>(*at) * w);
+}
+
+}  // namespace
+
+MLXONE_API int mlxone_route_experts(const void* x, int ld, const float* router, float* weights,
+                                    int tokens, int hidden, int experts, int top, int groups,
+                                    int keep, int group_score, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && hidden > 0 && experts > 0 && experts <= MAX_EXPERTS,
+                   "route_experts: 1 to %d experts", MAX_EXPERTS);
+    MLXONE_REQUIRE(groups > 0 && experts % groups == 0 && keep > 0 && keep <= groups,
+                   "route_experts: %d experts do not form %d groups of which %d are kept", experts,
+                   groups, keep);
+    MLXONE_REQUIRE(top > 0 && top <= 64 && top <= keep * (experts / groups) && group_score > 0,
+                   "route_experts: top %d of %d allowed experts", top, keep * (experts / groups));
+    if (dtype == MLXONE_BF16)
+        launch_kernel(route_experts_kernel<__nv_bfloat16>, dim3(tokens), dim3(ROUTE_THREADS), 0,
+                      stream, true, (const __nv_bfloat16*)x, ld, router, weights, hidden, experts, top,
+                      groups, keep, group_score);
+    else
+        launch_kernel(route_experts_kernel<float>, dim3(tokens), dim3(ROUTE_THREADS), 0, stream, true,
+                      (const float*)x, ld, router, weights, hidden, experts, top, groups, keep,
+                      group_score);
+    MLXONE_LAUNCH_CHECK("route_experts");
+    return 0;
+}
+
+MLXONE_API int mlxone_scale_expert_columns(void* x, int ld, const float* weights, int tokens,
+                                           int experts, int width, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && experts > 0 && width > 0 && ld >= experts * width,
+                   "scale_expert_columns: bad sizes");
+    const long long total = (long long)tokens * experts * width;
+    const int blocks = ceil_div_host(total, 256);
+    if (dtype == MLXONE_BF16)
+        launch_kernel(scale_expert_columns_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                      true, (__nv_bfloat16*)x, ld, weights, experts, width, total);
+    else
+        launch_kernel(scale_expert_columns_kernel<float>, dim3(blocks), dim3(256), 0, stream, true,
+                      (float*)x, ld, weights, experts, width, total);
+    MLXONE_LAUNCH_CHECK("scale_expert_columns");
+    return 0;
+}

@@ -4,11 +4,13 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------ add vectors
-// residual[t, :] += delta[t, :] (if delta) + table[ids[t], :] (if table) + vector[:] (if vector).
+// residual[t, :] += delta_scale * delta[t, :] (if delta) + table[ids[t], :] (if table) +
+// vector[:] (if vector).
 template <typename T>
 __global__ void add_vectors_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const int* __restrict__ ids, const T* __restrict__ table,
-                                   const float* __restrict__ vector, int hidden, int vocab) {
+                                   const float* __restrict__ vector, int hidden, int vocab,
+                                   float delta_scale) {
     griddep_launch();
     griddep_wait();
     const int t = blockIdx.x;
@@ -21,7 +23,7 @@ __global__ void add_vectors_kernel(float* __restrict__ residual, const T* __rest
     float* dst = residual + (size_t)t * hidden;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float v = dst[c];
-        if (delta != nullptr) v += to_float<T>(delta[(size_t)t * hidden + c]);
+        if (delta != nullptr) v = fmaf(delta_scale, to_float<T>(delta[(size_t)t * hidden + c]), v);
         if (row != nullptr) v += to_float<T>(row[c]);
         if (vector != nullptr) v += vector[c];
         dst[c] = v;
@@ -30,7 +32,7 @@ __global__ void add_vectors_kernel(float* __restrict__ residual, const T* __rest
 
 MLXONE_API int mlxone_add_vectors(float* residual, const void* delta, const int* ids,
                                   const void* table, const float* vector, int tokens, int hidden,
-                                  int vocab, int dtype, cudaStream_t stream) {
+                                  int vocab, int dtype, float delta_scale, cudaStream_t stream) {
     if (tokens == 0) return 0;
     MLXONE_REQUIRE(tokens > 0 && hidden > 0, "add_vectors: bad sizes");
     MLXONE_REQUIRE(table == nullptr || (ids != nullptr && vocab > 0), "add_vectors: a table needs ids");
@@ -38,11 +40,103 @@ MLXONE_API int mlxone_add_vectors(float* residual, const void* delta, const int*
     if (dtype == MLXONE_BF16)
         launch_kernel(add_vectors_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, true,
                       residual, (const __nv_bfloat16*)delta, ids, (const __nv_bfloat16*)table, vector,
-                      hidden, vocab);
+                      hidden, vocab, delta_scale);
     else
         launch_kernel(add_vectors_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true,
-                      residual, (const float*)delta, ids, (const float*)table, vector, hidden, vocab);
+                      residual, (const float*)delta, ids, (const float*)table, vector, hidden, vocab,
+                      delta_scale);
     MLXONE_LAUNCH_CHECK("add_vectors");
+    return 0;
+}
+
+// ------------------------------------------------------------------ stream beside embeddings
+// out[t, :hidden] = T(residual[t, :] + delta_scale * delta[t, :]), out[t, hidden:] =
+// table[ids[t], :]: the input of a product that mixes the stream with the tokens' embeddings.
+template <typename T>
+__global__ void concat_stream_kernel(const float* __restrict__ residual, const T* __restrict__ delta,
+                                     const int* __restrict__ ids, const T* __restrict__ table,
+                                     T* __restrict__ out, int hidden, int vocab, float delta_scale) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = min(max(id, 0), vocab - 1);          // (the embedding kernel has reported a bad id)
+    const T* row = table + (size_t)id * hidden;
+    const float* src = residual + (size_t)t * hidden;
+    T* dst = out + (size_t)t * 2 * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = src[c];
+        if (delta != nullptr) v = fmaf(delta_scale, to_float<T>(delta[(size_t)t * hidden + c]), v);
+        dst[c] = from_float<T>(v);
+        dst[hidden + c] = row[c];
+    }
+}
+
+MLXONE_API int mlxone_concat_stream(const float* residual, const void* delta, const int* ids,
+                                    const void* table, void* out, int tokens, int hidden, int vocab,
+                                    int dtype, float delta_scale, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && hidden > 0 && vocab > 0, "concat_stream: bad sizes");
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == MLXONE_BF16)
+        launch_kernel(concat_stream_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
+                      true, residual, (const __nv_bfloat16*)delta, ids, (const __nv_bfloat16*)table,
+                      (__nv_bfloat16*)out, hidden, vocab, delta_scale);
+    else
+        launch_kernel(concat_stream_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true,
+                      residual, (const float*)delta, ids, (const float*)table, (float*)out, hidden,
+                      vocab, delta_scale);
+    MLXONE_LAUNCH_CHECK("concat_stream");
+    return 0;
+}
+
+// ------------------------------------------------------------------ soft cap
+// x = cap * tanh(x / cap), in place, 32-bit.
+__global__ void softcap_kernel(float* __restrict__ x, long long total, float cap, float inverse) {
+    griddep_launch();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] * inverse);
+}
+
+MLXONE_API int mlxone_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total == 0) return 0;
+    MLXONE_REQUIRE(total > 0 && cap > 0.f, "softcap: bad arguments");
+    launch_kernel(softcap_kernel, dim3(ceil_div_host(total, 256)), dim3(256), 0, stream, true, x,
+                  total, cap, 1.f / cap);
+    MLXONE_LAUNCH_CHECK("softcap");
+    return 0;
+}
+
+// ------------------------------------------------------------------ gate with any activation
+// out[t, f] = act(gate_up[t, f]) * gate_up[t, width + f], in 32-bit.
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width,
+                                        long long total, int kind) {
+    griddep_launch();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / width;
+    const int f = (int)(i - t * width);
+    const float gate = to_float<T>(gate_up[t * 2 * width + f]);
+    const float up = to_float<T>(gate_up[t * 2 * width + width + f]);
+    out[i] = from_float<T>(mlxone_activate(gate, kind) * up);
+}
+
+MLXONE_API int mlxone_gated_activation(const void* gate_up, void* out, int rows, int width, int kind,
+                                       int dtype, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    MLXONE_REQUIRE(rows > 0 && width > 0 && kind >= 0 && kind <= 3, "gated_activation: bad arguments");
+    const long long total = (long long)rows * width;
+    const int blocks = ceil_div_host(total, 256);
+    if (dtype == MLXONE_BF16)
+        launch_kernel(gated_activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true,
+                      (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total, kind);
+    else
+        launch_kernel(gated_activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, true,
+                      (const float*)gate_up, (float*)out, width, total, kind);
+    MLXONE_LAUNCH_CHECK("gated_activation");
     return 0;
 }
 

@@ -57,6 +57,7 @@ class CudaOps:
         self.lib.mlxone_last_error.restype = ctypes.c_char_p
         self.lib.mlxone_gated_delta_scratch.restype = ctypes.c_longlong
         self.lib.mlxone_gated_delta_state.restype = ctypes.c_longlong
+        self.lib.mlxone_lightning_scratch.restype = ctypes.c_longlong
         if self.lib.mlxone_abi_version() != 1:
             raise KernelBuildError("the CUDA extension is of another version; rebuild it")
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -181,7 +182,7 @@ class CudaOps:
                    _c_void_p(_ptr(self.error_flag)))
         return out
 
-    def add_rmsnorm(self, residual, delta, weight, eps, dtype):
+    def add_rmsnorm(self, residual, delta, weight, eps, dtype, delta_scale=1.0):
         self._need(residual, torch.float32, "residual")
         self._need(weight, torch.float32, "norm weight")
         if delta is not None:
@@ -194,7 +195,7 @@ class CudaOps:
         out = torch.empty((rows, hidden), dtype=dtype, device=self.device)
         self._call("mlxone_add_rmsnorm", _c_void_p(_ptr(residual)), _c_void_p(_ptr(delta)),
                    _c_void_p(_ptr(weight)), _c_void_p(_ptr(out)), _c_int(rows), _c_int(hidden),
-                   _c_float(eps), _c_int(_dtype_code(dtype)))
+                   _c_float(eps), _c_int(_dtype_code(dtype)), _c_float(delta_scale))
         return out
 
     def gather_rows(self, residual, delta, rows):
@@ -378,15 +379,23 @@ class CudaOps:
             return out
         return self.swiglu(self.linear(a, gate_up))
 
-    def linear_add(self, a, w, bias, residual):
-        """Adds a @ w^T (+ bias) to the float32 ``residual``. Returns None if it was added in
-        place (few rows: the product's epilogue does it), else the product, which the caller
-        adds with the next norm."""
+    def linear_add(self, a, w, bias, residual, scale=1.0):
+        """Adds scale * (a @ w^T (+ bias)) to the float32 ``residual``. Returns None if it was
+        added in place (few rows: the product's epilogue does it), else the product, which the
+        caller adds, with its factor, with the next norm."""
         self._check_product(a, w)
         if self._skinny(a, w, fused=True):
             self._need(residual, torch.float32, "residual")
-            self._skinny_call(a, w, bias, residual, residual.shape[1], self._ADD)
+            if scale == 1.0:
+                self._skinny_call(a, w, bias, residual, residual.shape[1], self._ADD)
+            else:
+                self._call("mlxone_gemm_skinny_scaled_add", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
+                           _c_void_p(_ptr(w)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(residual)),
+                           _c_int(residual.shape[1]), _c_int(a.shape[0]), _c_int(w.shape[0]),
+                           _c_int(a.shape[1]), _c_float(scale))
             return None
+        if scale != 1.0:
+            return self.linear(a, w, bias)
         if self._swapped(a, w):
             self._need(residual, torch.float32, "residual")
             self._swapped_call(a, w, bias, residual, residual.shape[1], self._ADD)
@@ -396,6 +405,23 @@ class CudaOps:
             self._tcgen05_call(a, w, bias, residual, residual.shape[1], self._ADD)
             return None
         return self.linear(a, w, bias)
+
+    def linear_gated(self, a, gate_up, kind):
+        """act(a @ gate^T) * (a @ up^T) with gate_up = [gate rows; up rows], for the activations
+        of ``ACTIVATIONS``: silu takes the fused kernels of ``linear_swiglu``; the others run the
+        product (with the norm of its input applied while loading, for few rows) and one kernel
+        for the gate."""
+        if kind == "silu":
+            return self.linear_swiglu(a, gate_up)
+        if kind not in self.ACTIVATIONS:
+            raise KernelError(f"unknown activation {kind!r}")
+        both = self.linear(a, gate_up)
+        rows, twice = both.shape
+        out = torch.empty((rows, twice // 2), dtype=both.dtype, device=self.device)
+        self._call("mlxone_gated_activation", _c_void_p(_ptr(both)), _c_void_p(_ptr(out)),
+                   _c_int(rows), _c_int(twice // 2), _c_int(self.ACTIVATIONS[kind]),
+                   _c_int(_dtype_code(both.dtype)))
+        return out
 
     # ---- activations of a feed-forward without a gate
 
@@ -431,9 +457,9 @@ class CudaOps:
 
     # ---- the 32-bit stream
 
-    def add_vectors(self, residual, delta, token_ids, table, vector):
-        """In place: residual[t] += delta[t] (if given) + table[token_ids[t]] (if a table is
-        given) + vector (if given; float32 [hidden])."""
+    def add_vectors(self, residual, delta, token_ids, table, vector, delta_scale=1.0):
+        """In place: residual[t] += delta_scale * delta[t] (if given) + table[token_ids[t]] (if a
+        table is given) + vector (if given; float32 [hidden])."""
         self._need(residual, torch.float32, "residual")
         tokens, hidden = residual.shape
         code = _F32
@@ -454,7 +480,90 @@ class CudaOps:
         self._call("mlxone_add_vectors", _c_void_p(_ptr(residual)), _c_void_p(_ptr(delta)),
                    _c_void_p(_ptr(token_ids)), _c_void_p(_ptr(table)), _c_void_p(_ptr(vector)),
                    _c_int(tokens), _c_int(hidden),
-                   _c_int(0 if table is None else table.shape[0]), _c_int(code))
+                   _c_int(0 if table is None else table.shape[0]), _c_int(code),
+                   _c_float(delta_scale))
+
+    def concat_stream(self, residual, delta, token_ids, table, dtype, delta_scale=1.0):
+        """[tokens, 2 hidden] in ``dtype``: the stream (with delta_scale * delta, if given) beside
+        the tokens' rows of ``table``."""
+        self._need(residual, torch.float32, "residual")
+        self._need(table, dtype, "table")
+        self._need(token_ids, torch.int32, "token ids")
+        tokens, hidden = residual.shape
+        if delta is not None:
+            self._need(delta, dtype, "delta")
+            if delta.shape != residual.shape:
+                raise KernelError("delta and residual differ in shape")
+        if table.shape[1] != hidden:
+            raise KernelError("table rows and residual rows differ in length")
+        out = torch.empty((tokens, 2 * hidden), dtype=dtype, device=self.device)
+        self._call("mlxone_concat_stream", _c_void_p(_ptr(residual)), _c_void_p(_ptr(delta)),
+                   _c_void_p(_ptr(token_ids)), _c_void_p(_ptr(table)), _c_void_p(_ptr(out)),
+                   _c_int(tokens), _c_int(hidden), _c_int(table.shape[0]),
+                   _c_int(_dtype_code(dtype)), _c_float(delta_scale))
+        return out
+
+    def softcap(self, logits, cap):
+        """In place: logits = cap * tanh(logits / cap) (float32)."""
+        self._need(logits, torch.float32, "logits")
+        self._call("mlxone_softcap", _c_void_p(_ptr(logits)), _c_ll(logits.numel()), _c_float(cap))
+
+    # ---- routed experts
+
+    def route_experts(self, x, router, *, experts, top, groups, keep, group_score):
+        """Routing weights float32 [tokens, experts] (zero for experts that were not chosen):
+        sigmoid scores of the 32-bit logits, the ``keep`` best of ``groups`` groups by the sum of
+        their ``group_score`` largest scores, the ``top`` best of their experts, normalised."""
+        self._need_rows(x, x.dtype, "x")
+        self._need(router, torch.float32, "router")
+        if router.shape != (experts, x.shape[1]):
+            raise KernelError("the router's shape does not match")
+        weights = torch.empty((x.shape[0], experts), dtype=torch.float32, device=self.device)
+        self._call("mlxone_route_experts", _c_void_p(_ptr(x)), _c_int(x.stride(0)),
+                   _c_void_p(_ptr(router)), _c_void_p(_ptr(weights)), _c_int(x.shape[0]),
+                   _c_int(x.shape[1]), _c_int(experts), _c_int(top), _c_int(groups), _c_int(keep),
+                   _c_int(group_score), _c_int(_dtype_code(x.dtype)))
+        return weights
+
+    def scale_expert_columns(self, gated, weights, width):
+        """In place: gated[t, e * width + f] *= weights[t, e]; columns beyond the experts' stay."""
+        self._need_rows(gated, gated.dtype, "gated")
+        self._need(weights, torch.float32, "weights")
+        self._call("mlxone_scale_expert_columns", _c_void_p(_ptr(gated)), _c_int(gated.stride(0)),
+                   _c_void_p(_ptr(weights)), _c_int(gated.shape[0]), _c_int(weights.shape[1]),
+                   _c_int(width), _c_int(_dtype_code(gated.dtype)))
+
+    # ---- lightning attention
+
+    def lightning_attention(self, projected, *, decay, norm_weight, eps, ctx, view, write, heads,
+                            key_dim, value_dim):
+        """From the fused projection [tokens, q | k | v | gate] to the mixer's gated output
+        [tokens, heads * value_dim]: silu, the recurrence S = decay S + k v^T, o = S^T q over each
+        request's tokens on its 32-bit state [heads, key_dim, value_dim], the norm over all heads
+        and the sigmoid gate."""
+        tokens = projected.shape[0]
+        self._need_rows(projected, projected.dtype, "projected")
+        inner = heads * value_dim
+        if projected.shape[1] != 2 * heads * key_dim + 2 * inner:
+            raise KernelError("the projection's width does not match the head counts")
+        for tensor, what in ((decay, "decay"), (norm_weight, "norm weight"), (view.state, "state")):
+            self._need(tensor, torch.float32, what)
+        if view.state[0].numel() != heads * key_dim * value_dim:
+            raise KernelError(f"a state slot has {view.state[0].numel()} values, the mixer needs "
+                              f"{heads * key_dim * value_dim}")
+        scratch = torch.empty(self.lib.mlxone_lightning_scratch(
+            tokens, ctx.requests, ctx.max_portion, heads, key_dim, value_dim),
+            dtype=torch.float32, device=self.device)
+        out = torch.empty((tokens, inner), dtype=projected.dtype, device=self.device)
+        self._call("mlxone_lightning", _c_void_p(_ptr(projected)), _c_int(projected.stride(0)),
+                   _c_void_p(_ptr(decay)), _c_void_p(_ptr(norm_weight)), _c_float(eps),
+                   _c_void_p(_ptr(view.state)), _c_void_p(_ptr(view.slots)),
+                   _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(scratch)),
+                   _c_void_p(_ptr(out)), _c_int(tokens), _c_int(ctx.requests),
+                   _c_int(ctx.max_portion), _c_int(heads), _c_int(key_dim), _c_int(value_dim),
+                   _c_int(1 if write else 0), _c_int(_dtype_code(projected.dtype)))
+        self.launches += 1 if ctx.max_portion < 128 else 3
+        return out
 
     def normed_mean_add(self, residual, outputs, weights, eps):
         """In place: residual += mean over branches of x / rms(x) * weight (rms over the row,
@@ -633,7 +742,7 @@ class CudaOps:
         return q
 
     def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
-                      scale, window, ctx, view, write, **extra):
+                      scale, window, ctx, view, write, sinks=None, **extra):
         """From the fused projection qkv [tokens, (heads + 2 kv_heads) * head_dim] to the mixed
         heads [tokens, heads * head_dim]: per-head norm of queries and keys, rotation, keys and
         values appended to the pages, attention. A step of single tokens in bfloat16 whose head
@@ -650,7 +759,7 @@ class CudaOps:
                                         rotary=rotary, ctx=ctx, view=view, write=write, **extra)
             return self.paged_attention(q, heads=heads, kv_heads=kv_heads,
                                         head_dim=view.kv.shape[-1], scale=scale, window=window,
-                                        ctx=ctx, view=view)
+                                        ctx=ctx, view=view, sinks=sinks)
         if (self.fused_decode_attention and qkv.dtype == torch.bfloat16
                 and ctx.max_portion == 1 and tokens == ctx.requests
                 and self.tensor_core_attention
@@ -672,7 +781,8 @@ class CudaOps:
                        _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(out)),
                        _c_void_p(_ptr(partial)), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
                        _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window or 0),
-                       _c_int(1 if write else 0), _c_void_p(_ptr(self.error_flag)))
+                       _c_int(1 if write else 0), _c_void_p(_ptr(sinks)),
+                       _c_void_p(_ptr(self.error_flag)))
             if partial is not None:
                 self.launches += 1          # the merge kernel
             return out
@@ -680,9 +790,10 @@ class CudaOps:
                                     q_weight=q_weight, k_weight=k_weight, eps=eps, rotary=rotary,
                                     ctx=ctx, view=view, write=write)
         return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
-                                    scale=scale, window=window, ctx=ctx, view=view)
+                                    scale=scale, window=window, ctx=ctx, view=view, sinks=sinks)
 
-    def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view):
+    def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view,
+                        sinks=None):
         """Attention of every token over its request's pages. bfloat16 with a head size that
         is a multiple of 16 up to 128 runs on tensor cores: the split-key decode kernel when
         every request brings one token, else the prefill kernel. Everything else (float32,
@@ -692,10 +803,15 @@ class CudaOps:
         width = view.block_table.shape[1]
         pages = view.kv.shape[1]
         code = _dtype_code(q.dtype)
+        if sinks is not None:
+            # (float32 [heads]: exp(sink) of a query's head stands in its softmax's denominator)
+            self._need(sinks, torch.float32, "sinks")
+            if sinks.numel() != heads:
+                raise KernelError("one sink per query head")
         if self.tensor_core_attention and self.lib.mlxone_attention_mma_supports(head_dim, code):
             if ctx.max_portion == 1 and tokens == ctx.requests:
                 self._decode_attention(q, out, ctx.requests, heads, kv_heads, head_dim, scale,
-                                       window, ctx, view)
+                                       window, ctx, view, sinks)
                 return out
             # The decodes at the head of a mixed step go to the split-key kernel, which reads
             # each request's keys once for all its query heads; as one-token portions in the
@@ -705,13 +821,13 @@ class CudaOps:
                 singles = 0
             if singles:
                 self._decode_attention(q, out, singles, heads, kv_heads, head_dim, scale, window,
-                                       ctx, view)
+                                       ctx, view, sinks)
             # the other requests: the tables, starts and histories from request ``singles`` on
             # (token numbers in request_start stay those of the whole step)
             rest = ctx.requests - singles
             table = view.block_table[singles:]
             starts, history = ctx.request_start[singles:], ctx.history[singles:]
-            if (self.tcgen05_attention and q.dtype == torch.bfloat16
+            if (self.tcgen05_attention and q.dtype == torch.bfloat16 and sinks is None
                     and self.lib.mlxone_attention_tcgen05_supports(
                         _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):
                 # few query tiles (a prompt's portion beside a step's decodes): their keys are
@@ -749,7 +865,7 @@ class CudaOps:
                            _c_void_p(_ptr(starts)), _c_void_p(_ptr(history)),
                            _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
                            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
-                           _c_int(window or 0))
+                           _c_int(window or 0), _c_void_p(_ptr(sinks)))
             return out
         self._call("mlxone_attention_generic", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
                    _c_void_p(_ptr(view.block_table)), _c_int(width),
@@ -757,21 +873,22 @@ class CudaOps:
                    _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(ctx.token_request)),
                    _c_void_p(_ptr(out)), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
                    _c_int(head_dim), _c_float(scale), _c_int(window or 0),
-                   _c_int(code), _c_void_p(_ptr(self.error_flag)))
+                   _c_int(code), _c_void_p(_ptr(sinks)), _c_void_p(_ptr(self.error_flag)))
         return out
 
     def _decode_attention(self, q, out, requests, heads, kv_heads, head_dim, scale, window, ctx,
-                          view) -> None:
+                          view, sinks=None) -> None:
         """The split-key kernel for the first ``requests`` requests of the step, one token each
         (token i is request i's): rows 0 to requests - 1 of q, positions, table and out."""
         width = view.block_table.shape[1]
         splits, partial = self._decode_plan(requests, heads, kv_heads, head_dim, width, window,
                                             view)
-        self._call("mlxone_attention_decode", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
+        self._call("mlxone_attention_decode_sinks", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
                    _c_void_p(_ptr(view.block_table)), _c_int(width), _c_int(view.page_size),
                    _c_int(view.kv.shape[1]), _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(out)),
                    _c_void_p(_ptr(partial)), _c_int(requests), _c_int(heads), _c_int(kv_heads),
-                   _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window or 0))
+                   _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window or 0),
+                   _c_void_p(_ptr(sinks)))
         if partial is not None:
             self.launches += 1          # the merge kernel
 

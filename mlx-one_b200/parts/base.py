@@ -147,6 +147,11 @@ class Part:
     # contents (it reads ``StepContext.host``, copies to the host, or loops over requests in
     # Python). A model that holds such a part runs every step eagerly.
     capturable = True
+    # The factor on this part's output where it enters the 32-bit stream. The block that
+    # arranges the part sets it; a mixer or feed-forward that adds its output into the stream
+    # itself (``fuses_residual``) and honours the factor says so with ``scales_residual``.
+    residual_scale = 1.0
+    scales_residual = False
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor],
                  runtime: Runtime) -> None:
@@ -219,10 +224,10 @@ class Norm(Part):
     supports_lazy = False
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None,
-                lazy: bool = False) -> torch.Tensor:
-        """Adds ``delta`` (compute dtype, or None) into the 32-bit ``residual`` in place
-        and returns the normed residual in the compute dtype. With ``lazy`` a norm may return
-        a ``NormedInput`` instead, for a consumer that ``accepts_normed_input``."""
+                lazy: bool = False, delta_scale: float = 1.0) -> torch.Tensor:
+        """Adds ``delta_scale * delta`` (compute dtype, or None) into the 32-bit ``residual`` in
+        place and returns the normed residual in the compute dtype. With ``lazy`` a norm may
+        return a ``NormedInput`` instead, for a consumer that ``accepts_normed_input``."""
         raise NotImplementedError
 
 
@@ -248,9 +253,14 @@ class Block(Part):
         self.feed_forward = feed_forward
         self.feed_forward_norm = feed_forward_norm
 
+    # the factor with which the output that ``forward`` returns is still to be added
+    pending_scale = 1.0
+
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx: StepContext,
                 cache: Any, write: bool) -> torch.Tensor | None:
         """``residual`` is the 32-bit stream [tokens, hidden], updated in place; ``delta``
         is an output of the previous block that is still to be added (or None). Returns
-        this block's pending output in the same way."""
+        this block's pending output in the same way. A block that takes ``delta_scale=`` is
+        given the factor on ``delta`` when that is not 1 (the ``pending_scale`` of the block
+        before it)."""
         raise NotImplementedError

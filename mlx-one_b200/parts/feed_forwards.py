@@ -11,8 +11,9 @@ from .spec import TensorSpec
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
-    """w2(silu(w1 x) * w3 x), no biases. Parameters: ``hidden``, ``width``. The gate and
-    up matrices are stacked at load time so that one matrix product feeds the gate kernel.
+    """w2(act(w1 x) * w3 x), no biases. Parameters: ``hidden``, ``width``, ``activation`` of the
+    gate (``silu``, the default, or ``gelu_tanh``, ``relu``, ``relu2``). The gate and up matrices
+    are stacked at load time so that one matrix product feeds the gate kernel.
     Reference: src/mlx_one/models/language/lfm2/reference_math.py:114-135."""
 
     @classmethod
@@ -27,16 +28,23 @@ class SwiGLU(FeedForward):
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
         self.width = spec["width"]
+        self.activation = spec.get("activation") or "silu"
         self.gate_up = self.matrix(torch.cat([tensors["w1.weight"], tensors["w3.weight"]], dim=0))
         self.down = self.matrix(tensors["w2.weight"])
 
     fuses_residual = True
+    scales_residual = True
     accepts_normed_input = True
 
     def forward(self, x, ctx, residual=None):
-        gated = self.ops.linear_swiglu(x, self.gate_up)
+        if self.activation == "silu":
+            gated = self.ops.linear_swiglu(x, self.gate_up)
+        else:
+            gated = self.ops.linear_gated(x, self.gate_up, self.activation)
         if residual is None:
             return self.ops.linear(gated, self.down)
+        if self.residual_scale != 1.0:
+            return self.ops.linear_add(gated, self.down, None, residual, scale=self.residual_scale)
         return self.ops.linear_add(gated, self.down, None, residual)
 
 
@@ -71,3 +79,72 @@ class DenseFeedForward(FeedForward):
         if residual is None:
             return self.ops.linear(hidden, self.down)
         return self.ops.linear_add(hidden, self.down, None, residual)
+
+
+@FEED_FORWARDS.register("routed")
+class RoutedExperts(FeedForward):
+    """A mixture of gated feed-forwards. Parameters: ``hidden``, ``width`` (of an expert),
+    ``experts``, ``top`` (experts a token uses), ``groups`` and ``keep`` (experts form ``groups``
+    equal runs of neighbours; a group's score is the sum of its ``group_score`` largest scores,
+    and only experts of the ``keep`` best groups can be chosen), ``shared_width`` (None: no
+    shared expert), ``activation`` of the gates, ``scores`` (``sigmoid``).
+
+    Router logits W_r x are 32-bit, scores s = sigmoid of them; the ``top`` allowed experts
+    with the largest scores are chosen and weighted with s / (sum of the chosen s + 1e-20). The
+    output is the weighted sum of the chosen experts' down(act(gate x) * up x), plus the shared
+    expert's, which every token uses with weight 1.
+
+    The experts' gate and up matrices are stacked into one matrix and their down matrices side
+    by side into another (the shared expert last). ``dense`` execution runs every token through
+    all of it: one product with the gate, the routing weights multiplied into the expert's
+    columns (zero for experts that were not chosen), one down product. ``sorted`` execution
+    (the kernels' grouped products over tokens sorted by expert) is used where the kernel set
+    offers it and it is cheaper."""
+
+    @classmethod
+    def tensors(cls, spec):
+        hidden, width = spec["hidden"], spec["width"]
+        out = {"router": TensorSpec((spec["experts"], hidden), "wide")}
+        for e in range(spec["experts"]):
+            out[f"e{e}.gate"] = TensorSpec((width, hidden))
+            out[f"e{e}.up"] = TensorSpec((width, hidden))
+            out[f"e{e}.down"] = TensorSpec((hidden, width))
+        if spec.get("shared_width"):
+            shared = spec["shared_width"]
+            out["shared.gate"] = TensorSpec((shared, hidden))
+            out["shared.up"] = TensorSpec((shared, hidden))
+            out["shared.down"] = TensorSpec((hidden, shared))
+        return out
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.experts, self.width = spec["experts"], spec["width"]
+        self.shared_width = spec.get("shared_width") or 0
+        self.activation = spec.get("activation") or "silu"
+        if (spec.get("scores") or "sigmoid") != "sigmoid":
+            raise ValueError("routing scores other than sigmoid are not built")
+        self.routing = dict(experts=self.experts, top=spec["top"], groups=spec.get("groups") or 1,
+                            keep=spec.get("keep") or 1, group_score=spec.get("group_score") or 2)
+        if self.experts % self.routing["groups"]:
+            raise ValueError("experts must form equal groups")
+        names = [f"e{e}." for e in range(self.experts)] + (["shared."] if self.shared_width else [])
+        self.gate_up = self.matrix(torch.cat([tensors[name + "gate"] for name in names] +
+                                             [tensors[name + "up"] for name in names], dim=0))
+        self.down = self.matrix(torch.cat([tensors[name + "down"] for name in names], dim=1))
+        self.router = tensors["router"].to(torch.float32).contiguous()
+
+    fuses_residual = True
+    scales_residual = True
+
+    def forward(self, x, ctx, residual=None):
+        weights = self.ops.route_experts(x, self.router, **self.routing)
+        if self.activation == "silu":
+            gated = self.ops.linear_swiglu(x, self.gate_up)
+        else:
+            gated = self.ops.linear_gated(x, self.gate_up, self.activation)
+        self.ops.scale_expert_columns(gated, weights, self.width)
+        if residual is None:
+            return self.ops.linear(gated, self.down)
+        if self.residual_scale != 1.0:
+            return self.ops.linear_add(gated, self.down, None, residual, scale=self.residual_scale)
+        return self.ops.linear_add(gated, self.down, None, residual)

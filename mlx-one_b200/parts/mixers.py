@@ -19,7 +19,9 @@ class Attention(Mixer):
     per-head RMSNorm of queries and keys), ``qk_norm`` (``weighted_before``: with a stored
     weight, before the rotation; ``plain_after``: without a weight, after the rotation),
     ``position`` (a position-encoding PartSpec), ``window`` (None = all keys), ``scale`` (None =
-    head_dim^-0.5).
+    head_dim^-0.5), ``sink`` (a stored number per query head, ``sink`` [heads], that stands in
+    the softmax's denominator as exp(sink) beside the keys' terms: it has no key and no value
+    and is not scaled).
 
     q, k, v projections (one fused matrix product), per-head RMSNorm of q and k, rotation,
     keys and values appended to the request's pages, causal softmax(q k^T scale) v where
@@ -63,11 +65,21 @@ class Attention(Mixer):
         if cls._norm_kind(spec) == "weighted_before":
             out["q_layernorm.weight"] = TensorSpec((hd,), "norm")
             out["k_layernorm.weight"] = TensorSpec((hd,), "norm")
+        if spec.get("sink"):
+            out["sink"] = TensorSpec((spec["heads"],), "wide")
         return out
 
     @classmethod
     def cache_need(cls, spec):
         return PagedKeyValues(spec["kv_heads"], cls._sizes(spec)[2], spec.get("window"))
+
+    def _reordered(self, weight, heads, order):
+        """The rows of a projection [heads * head_dim, hidden] in another order within each
+        head (queries and keys alike, so that their products stay what they were)."""
+        if order is None:
+            return weight
+        index = (torch.arange(heads)[:, None] * self.head_dim + order[None, :]).reshape(-1)
+        return weight[index.to(weight.device)]
 
     def __init__(self, spec, tensors, runtime):
         super().__init__(spec, tensors, runtime)
@@ -78,11 +90,19 @@ class Attention(Mixer):
         self.window = spec.get("window")
         scale = spec.get("scale")
         self.scale = float(self.head_dim ** -0.5 if scale is None else scale)
-        self.qkv = self.matrix(torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
+        position: PartSpec = spec.get("position") or PartSpec("none")
+        self.position = POSITIONS.get(position.kind)(position, {}, runtime)
+        # an encoding that pairs neighbouring dimensions: the kernels pair halves, so the rows
+        # of the query and key projections (and their biases) are put into that order once
+        order = getattr(self.position, "row_order", lambda size: None)(self.head_dim)
+        reorder = lambda name, heads: self._reordered(tensors[name], heads, order)
+        self.qkv = self.matrix(torch.cat([reorder("q_proj.weight", self.heads),
+                                          reorder("k_proj.weight", self.kv_heads),
                                           tensors["v_proj.weight"]], dim=0))
         self.qkv_bias = None
         if spec.get("bias"):
-            self.qkv_bias = self.vector(torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"],
+            self.qkv_bias = self.vector(torch.cat([reorder("q_proj.bias", self.heads),
+                                                   reorder("k_proj.bias", self.kv_heads),
                                                    tensors["v_proj.bias"]], dim=0))
         out = tensors["out_proj.weight"]
         if self.value_dim < self.row_dim:
@@ -97,8 +117,9 @@ class Attention(Mixer):
         if self.norm_kind == "weighted_before":
             self.q_norm = self.vector(tensors["q_layernorm.weight"])
             self.k_norm = self.vector(tensors["k_layernorm.weight"])
-        position: PartSpec = spec.get("position") or PartSpec("none")
-        self.position = POSITIONS.get(position.kind)(position, {}, runtime)
+            if order is not None:
+                self.q_norm = self.q_norm[order.to(self.q_norm.device)].contiguous()
+                self.k_norm = self.k_norm[order.to(self.k_norm.device)].contiguous()
         self.ops.check_attention_sizes(self.heads, self.kv_heads, self.row_dim)
         # what the plain form of the operation (one head size, weighted norm before a pure
         # rotation) does not cover goes to the kernels as extra arguments
@@ -107,8 +128,12 @@ class Attention(Mixer):
                 or self.position.amplitude() != 1.0):
             self.extra = dict(value_dim=self.value_dim, amplitude=self.position.amplitude(),
                               norm_after=self.norm_kind == "plain_after")
+        self.sinks = {}
+        if spec.get("sink"):
+            self.sinks = dict(sinks=self.vector(tensors["sink"]))
 
     fuses_residual = True
+    scales_residual = True
     accepts_normed_input = True
 
     def inner_parts(self):
@@ -127,9 +152,11 @@ class Attention(Mixer):
             qkv, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm, k_weight=self.k_norm, eps=self.eps,
             rotary=self.position.rotary_table(), scale=self.scale, window=self.window, ctx=ctx,
-            view=cache, write=write, **self.extra)
+            view=cache, write=write, **self.sinks, **self.extra)
         if residual is None:
             return self.ops.linear(mixed, self.out)
+        if self.residual_scale != 1.0:
+            return self.ops.linear_add(mixed, self.out, None, residual, scale=self.residual_scale)
         return self.ops.linear_add(mixed, self.out, None, residual)
 
 
@@ -266,6 +293,64 @@ class GatedDeltaRule(Mixer):
             write=write, **self.sizes)
         if residual is None:
             return self.ops.linear(mixed, self.out)
+        return self.ops.linear_add(mixed, self.out, None, residual)
+
+
+@MIXERS.register("lightning")
+class LightningAttention(Mixer):
+    """Linear attention with a constant decay per head. Parameters: ``hidden``, ``heads``,
+    ``key_dim``, ``value_dim``, ``decay`` (one number per head), ``eps`` (of the output norm).
+
+    q, k = silu(W x) [heads * key_dim], v = silu(W x) [heads * value_dim], head by head. Per
+    token and head S = decay_h S + k v^T and o = S^T q, with S [key_dim, value_dim] in 32-bit,
+    zero at a request's start and carried from token to token in the request's state slot. The
+    heads' outputs side by side are divided by their common root mean square (with ``eps``),
+    multiplied by ``norm`` [heads * value_dim] and by sigmoid(W_g x), and projected by W_o.
+    Everything after the projections' silu is 32-bit."""
+
+    @classmethod
+    def tensors(cls, spec):
+        hidden = spec["hidden"]
+        qk, inner = spec["heads"] * spec["key_dim"], spec["heads"] * spec["value_dim"]
+        return {"q": TensorSpec((qk, hidden)), "k": TensorSpec((qk, hidden)),
+                "v": TensorSpec((inner, hidden)), "g": TensorSpec((inner, hidden)),
+                "norm": TensorSpec((inner,), "norm"), "o": TensorSpec((hidden, inner))}
+
+    @classmethod
+    def cache_need(cls, spec):
+        return FixedState((spec["heads"] * spec["key_dim"] * spec["value_dim"],), "float32")
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.sizes = dict(heads=spec["heads"], key_dim=spec["key_dim"], value_dim=spec["value_dim"])
+        decay = [float(value) for value in spec["decay"]]
+        if len(decay) != spec["heads"]:
+            raise ValueError("one decay per head")
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(runtime.device)
+        # one product for everything that reads x: q | k | v | gate
+        self.project = self.matrix(torch.cat([tensors[name] for name in ("q", "k", "v", "g")], dim=0))
+        self.norm = self.vector(tensors["norm"])
+        self.out = self.matrix(tensors["o"])
+        self.eps = float(spec["eps"])
+
+    fuses_residual = True
+    scales_residual = True
+    accepts_normed_input = True
+
+    def input_projection(self):
+        return self.project, None
+
+    def forward(self, x, ctx, cache, write, residual=None):
+        return self.forward_projected(self.ops.linear(x, self.project), ctx, cache, write, residual)
+
+    def forward_projected(self, projected, ctx, cache, write, residual=None):
+        mixed = self.ops.lightning_attention(
+            projected, decay=self.decay, norm_weight=self.norm, eps=self.eps, ctx=ctx, view=cache,
+            write=write, **self.sizes)
+        if residual is None:
+            return self.ops.linear(mixed, self.out)
+        if self.residual_scale != 1.0:
+            return self.ops.linear_add(mixed, self.out, None, residual, scale=self.residual_scale)
         return self.ops.linear_add(mixed, self.out, None, residual)
 
 

@@ -128,6 +128,19 @@ class Model:
                 if not 0 <= call.inject.row < rows.shape[0]:
                     raise ValueError(f"{call.inject.vector} has no row {call.inject.row}")
                 self.injected[index] = rows[call.inject.row].to(torch.float32).contiguous()
+        # a matrix applied to the stream and the embeddings side by side before a call
+        self.mixing = {}
+        for index, call in enumerate(spec.order):
+            if call.inject is not None and call.inject.mix is not None:
+                matrix = tensors[call.inject.mix]
+                if tuple(matrix.shape) != (spec.hidden_size, 2 * spec.hidden_size):
+                    raise ValueError(f"{call.inject.mix} has shape {tuple(matrix.shape)}, expected "
+                                     f"{(spec.hidden_size, 2 * spec.hidden_size)}")
+                if call.inject.mix not in self.mixing:
+                    self.mixing[call.inject.mix] = matrix.to(runtime.dtype).contiguous()
+        self.softcap = None if spec.logit_softcap is None else float(spec.logit_softcap)
+        # the factor with which the pending output of the last forward is still to be added
+        self.pending_scale = 1.0
         self.cache_needs = cache_entries(spec)
         # whether steps of this model may be captured as CUDA graphs: every part says so
         parts = [self.final_norm]
@@ -144,22 +157,34 @@ class Model:
 
     def forward(self, ctx: StepContext):
         residual = self.ops.embedding(ctx.token_ids, self.embedding)
-        delta = None
+        delta, scale = None, 1.0
         if self.observer is not None:
             self.observer(-1, residual, delta)
         for place, call in enumerate(self.order):
-            if call.inject is not None:
+            extra = {} if delta is None or scale == 1.0 else {"delta_scale": scale}
+            if call.inject is not None and call.inject.mix is not None:
+                # the stream (with the pending output) and the token's embedding side by side in
+                # the compute dtype, one product back into a 32-bit stream, the pass's vector as
+                # the product's bias
+                both = self.ops.concat_stream(residual, delta, ctx.token_ids, self.embedding,
+                                              self.runtime.dtype, **extra)
+                residual = self.ops.linear(both, self.mixing[call.inject.mix],
+                                           self.injected.get(place), out_dtype=torch.float32)
+                delta, extra = None, {}
+            elif call.inject is not None:
                 # the pending output, the token's embedding once more and the pass's vector
                 # enter the 32-bit stream in one kernel
                 self.ops.add_vectors(residual, delta, ctx.token_ids,
                                      self.embedding if call.inject.embedding else None,
-                                     self.injected.get(place))
-                delta = None
-            delta = self.layers[call.layer].forward(residual, delta, ctx,
-                                                    view_of(ctx.views, call.cache),
-                                                    call.writes_cache)
+                                     self.injected.get(place), **extra)
+                delta, extra = None, {}
+            block = self.layers[call.layer]
+            delta = block.forward(residual, delta, ctx, view_of(ctx.views, call.cache),
+                                  call.writes_cache, **extra)
+            scale = block.pending_scale
             if self.observer is not None:
                 self.observer(place, residual, delta)
+        self.pending_scale = 1.0 if delta is None else scale
         return residual, delta
 
     def logits(self, residual, delta, rows: torch.Tensor | None) -> torch.Tensor:
@@ -170,11 +195,17 @@ class Model:
         else:
             picked, picked_delta = self.ops.gather_rows(residual, delta, rows)
         # the output product may apply the norm itself where the kernels can do that
+        extra = {}
+        if picked_delta is not None and self.pending_scale != 1.0:
+            extra["delta_scale"] = self.pending_scale
         if self.final_norm.supports_lazy:
-            normed = self.final_norm.forward(picked, picked_delta, lazy=True)
+            normed = self.final_norm.forward(picked, picked_delta, lazy=True, **extra)
         else:
-            normed = self.final_norm.forward(picked, picked_delta)
-        return self.ops.linear(normed, self.head, out_dtype=torch.float32)
+            normed = self.final_norm.forward(picked, picked_delta, **extra)
+        logits = self.ops.linear(normed, self.head, out_dtype=torch.float32)
+        if self.softcap is not None:
+            self.ops.softcap(logits, self.softcap)
+        return logits
 
     def weight_bytes(self) -> int:
         """Bytes of every matrix and vector a step reads once (a tied table counts once)."""

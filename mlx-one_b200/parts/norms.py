@@ -27,8 +27,11 @@ class RMSNorm(Norm):
             self.weight = (self.weight + float(spec["offset"])).contiguous()
         self.eps = float(spec["eps"])
 
-    def forward(self, residual, delta, lazy=False):
+    def forward(self, residual, delta, lazy=False, delta_scale=1.0):
         can_fuse = getattr(self.ops, "can_fuse_norm", None)
         if lazy and delta is None and can_fuse is not None and can_fuse(residual, self.runtime.dtype):
             return NormedInput(residual, self.weight, self.eps, self.runtime.dtype, self.ops)
-        return self.ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.runtime.dtype)
+        if delta is None or delta_scale == 1.0:
+            return self.ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.runtime.dtype)
+        return self.ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.runtime.dtype,
+                                    delta_scale=delta_scale)

@@ -71,6 +71,55 @@ class ScaledRotaryEncoding(PositionEncoding):
         return self.scale
 
 
+@POSITIONS.register("rope_long")
+class LongContextRotaryEncoding(PositionEncoding):
+    """Rotary encoding of the first ``rotary_dim`` dimensions of a head with f_i =
+    theta^(-2i / rotary_dim) and the long-context rule of Llama 3.1 for slow pairs: with the
+    wavelength l = 2 pi / f, pairs with l < original / high keep f, pairs with l > original / low
+    get f / factor, and between the two, with s = (original / l - low) / (high - low), the
+    frequency is (1 - s) f / factor + s f. Parameters: ``theta``, ``rotary_dim``, ``factor``,
+    ``original``, ``low``, ``high`` (``factor`` None: plain frequencies), and ``layout``:
+    ``halves`` (pair i is dimensions i and i + rotary_dim / 2) or ``neighbours`` (pair i is
+    dimensions 2i and 2i + 1). The kernels rotate halves; a mixer whose encoding pairs neighbours
+    reorders the rows of its query and key projections with ``row_order`` when it is built, which
+    leaves every score as it is. The table is worked out in 64-bit on the host and rounded once."""
+
+    LAYOUTS = ("halves", "neighbours")
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.rotary_dim = dims = int(spec["rotary_dim"])
+        if dims <= 0 or dims % 2:
+            raise ValueError("rotary_dim must be positive and even")
+        self.layout = spec.get("layout") or "halves"
+        if self.layout not in self.LAYOUTS:
+            raise ValueError(f"unknown layout {self.layout!r}")
+        theta = float(spec["theta"])
+        freq = theta ** (-2.0 * torch.arange(dims // 2, dtype=torch.float64) / dims)
+        factor = spec.get("factor")
+        if factor is not None:
+            factor, original = float(factor), float(spec["original"])
+            low, high = float(spec["low"]), float(spec["high"])
+            wave = 2 * math.pi / freq
+            blend = (original / wave - low) / (high - low)
+            mixed = (1 - blend) * freq / factor + blend * freq
+            freq = torch.where(wave < original / high, freq,
+                               torch.where(wave > original / low, freq / factor, mixed))
+        self.inv_freq = freq.to(torch.float32).to(runtime.device)
+
+    def rotary_table(self):
+        return self.inv_freq, self.rotary_dim
+
+    def row_order(self, head_dim: int) -> torch.Tensor | None:
+        """For a head of ``head_dim`` rows whose pairs are neighbours: the order of rows that
+        puts pair i at i and i + rotary_dim / 2 (None: nothing to reorder)."""
+        if self.layout == "halves":
+            return None
+        dims = self.rotary_dim
+        return torch.cat([torch.arange(0, dims, 2), torch.arange(1, dims, 2),
+                          torch.arange(dims, head_dim)])
+
+
 @POSITIONS.register("none")
 class NoPositionEncoding(PositionEncoding):
     """No rotation: order is known to the model only through causality."""

@@ -59,11 +59,15 @@ class LayerSpec:
 class Injection:
     """Something added to every token's residual stream right before a call of the order:
     row ``row`` of the stored tensor ``vector`` ([rows, hidden], listed in
-    ``ModelSpec.vectors``), and, with ``embedding``, the token's embedding once more."""
+    ``ModelSpec.vectors``), and, with ``embedding``, the token's embedding once more.
+    With ``mix`` (the stored name of a [hidden, 2 hidden] matrix, also listed in
+    ``ModelSpec.vectors``) the stream is first replaced by that matrix applied to the stream and
+    the token's embedding side by side (stream first); the vector's row is added to the result."""
 
     vector: str | None = None
     row: int = 0
     embedding: bool = False
+    mix: str | None = None
 
 
 @dataclass(frozen=True)
@@ -98,3 +102,5 @@ class ModelSpec:
     rename: Callable[[str, tuple[int, ...]], tuple[str, int | None] | None] | None = None
     # stored tensors that belong to no part (what ``Injection.vector`` names): name -> TensorSpec
     vectors: Mapping[str, Any] = field(default_factory=dict)
+    # logits become cap * tanh(logits / cap); None: the output product's values as they are
+    logit_softcap: float | None = None

@@ -35,9 +35,9 @@ class PlainOps:
     def embedding(self, ids, table):
         return table[ids.long()].float()
 
-    def add_rmsnorm(self, residual, delta, weight, eps, dtype):
+    def add_rmsnorm(self, residual, delta, weight, eps, dtype, delta_scale=1.0):
         if delta is not None:
-            residual += delta.float()
+            residual += delta.float() * delta_scale
         inv = torch.rsqrt(residual.pow(2).mean(dim=-1, keepdim=True) + eps)
         return (residual * inv * weight).to(dtype)
 
@@ -56,8 +56,13 @@ class PlainOps:
     def linear_swiglu(self, a, gate_up):
         return self.swiglu(self.linear(a, gate_up))
 
-    def linear_add(self, a, w, bias, residual):
-        return self.linear(a, w, bias)
+    def linear_add(self, a, w, bias, residual, scale=1.0):
+        return self.linear(a, w, bias)      # (the caller adds it, with its factor)
+
+    def linear_gated(self, a, gate_up, kind):
+        both = self.linear(a, gate_up)
+        width = both.shape[1] // 2
+        return (self.activation(both[:, :width], kind).float() * both[:, width:].float()).to(a.dtype)
 
     def swiglu(self, gate_up):
         width = gate_up.shape[1] // 2
@@ -146,16 +151,66 @@ class PlainOps:
         return q.contiguous()
 
     def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
-                      scale, window, ctx, view, write, **extra):
+                      scale, window, ctx, view, write, sinks=None, **extra):
         q = self.qk_norm_rope_store(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
                                     q_weight=q_weight, k_weight=k_weight, eps=eps, rotary=rotary,
                                     ctx=ctx, view=view, write=write, **extra)
         return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=view.kv.shape[-1],
-                                    scale=scale, window=window, ctx=ctx, view=view)
+                                    scale=scale, window=window, ctx=ctx, view=view, sinks=sinks)
 
-    def add_vectors(self, residual, delta, token_ids, table, vector):
+    def concat_stream(self, residual, delta, token_ids, table, dtype, delta_scale=1.0):
+        stream = residual if delta is None else residual + delta.float() * delta_scale
+        return torch.cat([stream.to(dtype), table[token_ids.long()].to(dtype)], dim=1)
+
+    def softcap(self, logits, cap):
+        logits.copy_(cap * torch.tanh(logits / cap))
+
+    def route_experts(self, x, router, *, experts, top, groups, keep, group_score):
+        scores = torch.sigmoid(x.float() @ router.T)
+        tokens, per = scores.shape[0], experts // groups
+        weights = torch.zeros_like(scores)
+        for t in range(tokens):
+            row = scores[t]
+            best = sorted(range(groups), key=lambda g: (
+                -float(row[g * per:(g + 1) * per].topk(min(group_score, per)).values.sum()), g))[:keep]
+            allowed = [e for e in range(experts) if e // per in best]
+            chosen = sorted(allowed, key=lambda e: (-float(row[e]), e))[:top]
+            total = sum(float(row[e]) for e in chosen) + 1e-20
+            for e in chosen:
+                weights[t, e] = float(row[e]) / total
+        return weights
+
+    def scale_expert_columns(self, gated, weights, width):
+        experts = weights.shape[1]
+        scaled = gated[:, :experts * width].float().view(-1, experts, width) * weights[:, :, None]
+        gated[:, :experts * width] = scaled.view(-1, experts * width).to(gated.dtype)
+
+    def lightning_attention(self, projected, *, decay, norm_weight, eps, ctx, view, write, heads,
+                            key_dim, value_dim):
+        tokens = projected.shape[0]
+        qk, inner = heads * key_dim, heads * value_dim
+        flat = projected.float()
+        silu = lambda z: z / (1 + torch.exp(-z))
+        q = silu(flat[:, :qk]).view(tokens, heads, key_dim)
+        k = silu(flat[:, qk:2 * qk]).view(tokens, heads, key_dim)
+        v = silu(flat[:, 2 * qk:2 * qk + inner]).view(tokens, heads, value_dim)
+        gate = torch.sigmoid(flat[:, 2 * qk + inner:])
+        out = torch.empty(tokens, heads, value_dim)
+        starts, slots = ctx.request_start.tolist(), view.slots.tolist()
+        for r in range(ctx.requests):
+            state = view.state[slots[r]].view(heads, key_dim, value_dim).clone()
+            for t in range(starts[r], starts[r + 1]):
+                state = decay[:, None, None] * state + k[t][:, :, None] * v[t][:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", state, q[t])
+            if write:
+                view.state[slots[r]] = state.reshape(-1)
+        out = out.reshape(tokens, inner)
+        out = out * torch.rsqrt(out.pow(2).mean(dim=-1, keepdim=True) + eps) * norm_weight * gate
+        return out.to(projected.dtype)
+
+    def add_vectors(self, residual, delta, token_ids, table, vector, delta_scale=1.0):
         if delta is not None:
-            residual += delta.float()
+            residual += delta.float() * delta_scale
         if table is not None:
             residual += table[token_ids.long()].float()
         if vector is not None:
@@ -232,7 +287,8 @@ class PlainOps:
         out = out * silu(gate)
         return out.reshape(tokens, inner).to(projected.dtype)
 
-    def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view):
+    def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view,
+                        sinks=None):
         tokens = q.shape[0]
         out = torch.empty(tokens, heads, head_dim)
         positions = ctx.positions.tolist()
@@ -251,6 +307,10 @@ class PlainOps:
             k = k.repeat_interleave(group, dim=1)
             v = v.repeat_interleave(group, dim=1)
             scores = torch.einsum("hd,khd->hk", q[t].float(), k) * scale
+            if sinks is not None:
+                # a column without a key or a value: it only takes its share of the weights
+                scores = torch.cat([scores, sinks.float()[:, None]], dim=1)
+                v = torch.cat([v, torch.zeros_like(v[:1])], dim=0)
             out[t] = torch.einsum("hk,khd->hd", torch.softmax(scores, dim=-1), v)
         return out.reshape(tokens, heads * head_dim).to(q.dtype)
 
