@@ -113,10 +113,12 @@ def decayed_outer_product_state(q, k, v, decay):
     return o
 
 
-def routing(h, router, experts, top, groups, keep):
+def routing(h, router, experts, top, groups, keep, margins=None):
     """Weights [T, experts]: sigmoid scores; experts in ``groups`` equal runs of neighbours, a
     group's score the sum of its two largest, only the best ``keep`` groups stay; of those the
-    ``top`` largest are chosen, their scores divided by their sum."""
+    ``top`` largest are chosen, their scores divided by their sum. ``margins`` collects, per
+    token, how far the choice is from another one: the gap between the worst kept and the best
+    dropped group, and between the worst chosen and the best allowed expert that was not."""
     s = torch.sigmoid(h @ router.T)
     T = s.shape[0]
     per = experts // groups
@@ -128,6 +130,15 @@ def routing(h, router, experts, top, groups, keep):
     chosen = s.masked_fill(~allowed, -1.0).topk(top, dim=-1).indices
     weights = torch.zeros_like(s)
     weights.scatter_(1, chosen, s.gather(1, chosen))
+    if margins is not None:
+        gap = torch.full((T,), math.inf, dtype=s.dtype)
+        if keep < groups:
+            ranked = group_score.sort(dim=-1, descending=True).values
+            gap = torch.minimum(gap, ranked[:, keep - 1] - ranked[:, keep])
+        ranked = s.masked_fill(~allowed, -1.0).sort(dim=-1, descending=True).values
+        if top < keep * per:
+            gap = torch.minimum(gap, ranked[:, top - 1] - ranked[:, top])
+        margins.append(gap)
     return weights / (weights.sum(-1, keepdim=True) + 1e-20)
 
 
@@ -141,7 +152,8 @@ def attention_mixer(h, w, p, c):
     q = rotate_neighbours((h @ w[p + "q"].T).view(T, H, D), positions, c.get("rot"))
     k = rotate_neighbours((h @ w[p + "k"].T).view(T, G, D), positions, c.get("rot"))
     v = (h @ w[p + "v"].T).view(T, G, V)
-    mixed = windowed_attention_with_sink(q, k, v, c["scale"], c["mask"]["size"], w[p + "sink"])
+    window = (c.get("mask") or {}).get("size") or T
+    mixed = windowed_attention_with_sink(q, k, v, c["scale"], window, w[p + "sink"])
     return mixed.reshape(T, H * V) @ w[p + "o"].T
 
 
@@ -160,10 +172,11 @@ def gated_feed_forward(h, w, p, act):
     return (act(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def routed_feed_forward(h, w, p, c):
+def routed_feed_forward(h, w, p, c, margins=None):
     r = c["router"]
-    weights = routing(h, w[p + "router"], r["experts"], r["top"], r["groups"]["count"],
-                      r["groups"]["keep"])
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    weights = routing(h, w[p + "router"], r["experts"], r["top"], groups["count"], groups["keep"],
+                      margins)
     out = torch.zeros_like(h)
     for e in range(r["experts"]):
         out = out + weights[:, e:e + 1] * gated_feed_forward(h, w, f"{p}e{e}.", silu)
@@ -188,9 +201,10 @@ def layer_runs(cfg):
     return runs + [(i, None) for i in range(loop["stop"], count)]
 
 
-def forward(cfg, w, tokens, states=None):
-    """Logits [T, vocab] of a whole sequence; ``states`` collects the stream after each run."""
-    eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
+def forward(cfg, w, tokens, states=None, margins=None):
+    """Logits [T, vocab] of a whole sequence; ``states`` collects the stream after each run,
+    ``margins`` the routing margins of every routed feed-forward that runs."""
+    eps, m = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     x = w["embed"][torch.as_tensor(tokens)]
     embedded = x.clone()
     for index, turn in layer_runs(cfg):
@@ -210,7 +224,7 @@ def forward(cfg, w, tokens, states=None):
             if mlp["kind"] == "dense":
                 x = x + m * gated_feed_forward(h, w, p + "mlp.", gelu_tanh)
             elif mlp["kind"] == "moe":
-                x = x + m * routed_feed_forward(h, w, p + "mlp.", mlp)
+                x = x + m * routed_feed_forward(h, w, p + "mlp.", mlp, margins)
             else:
                 raise ValueError(mlp["kind"])
         if states is not None:
@@ -226,8 +240,21 @@ class PlainModel:
         self.w = {name: t.to(kind) for name, t in
                   read_tensors(Path(model_dir) / "model.safetensors").items()}
 
+        self.w32 = {name: t.to(torch.float32) for name, t in self.w.items()} \
+            if kind == torch.float64 else None
+
     def logits(self, tokens, states=None):
-        return forward(self.cfg, self.w, tokens, states).float()
+        """Logits [T, vocab]. The result carries ``noise`` [T], how far the same equations in
+        32-bit arithmetic land from the 64-bit ones at each position (largest difference of a
+        logit), and ``margin`` [T], the smallest routing margin of the position (infinite
+        without routed layers): a position whose margin is tiny is decided by rounding."""
+        margins = []
+        out = forward(self.cfg, self.w, tokens, states, margins).float()
+        out.margin = torch.stack(margins).amin(0).float() if margins \
+            else torch.full((len(tokens),), math.inf)
+        if self.w32 is not None:
+            out.noise = (forward(self.cfg, self.w32, tokens) - out).abs().amax(dim=-1)
+        return out
 
     def greedy(self, prompt, count):
         tokens = list(prompt)
