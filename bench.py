@@ -17,6 +17,8 @@ Two more workloads, each printing one JSON line of its own (the default line is 
 
     python bench.py --case batching     continuous batching of 128 requests at the LFM2-700M shape
     python bench.py --case long         4 x 32,768-token prompts at the LFM2-350M shape, then decoding
+    python bench.py --case farorax      Farorax beside Galarax at equal width, depth and vocabulary:
+                                        decode and prefill tokens/s, and the new kernels alone
     python bench.py --case galarax      Galarax beside LFM2 at equal width, depth and vocabulary:
                                         decode and prefill throughput, and its new kernels alone
 
@@ -201,11 +203,22 @@ def model_flops(spec, tokens):
     """Matrix-product and attention flops of one whole-prompt step (one logits row)."""
     from mlx_one_b200.parts.model import expected_tensors
 
+    import re
+
     flops = 0
+    used = {}                   # layer prefix -> share of its routed experts that a token uses
+    for layer in spec.layers:
+        part = layer.feed_forward
+        if part is not None and part.kind == "routed":
+            used[layer.prefix + part.prefix] = part["top"] / part["experts"]
     for name, tensor in expected_tensors(spec).items():
         if len(tensor.shape) == 2 and name != spec.embedding and name != spec.head \
-                and not name.endswith(("conv.conv", ".conv")) and name not in spec.vectors:
-            flops += 2 * tokens * tensor.shape[0] * tensor.shape[1]
+                and not name.endswith(("conv.conv", ".conv", ".router")) and name not in spec.vectors:
+            share = 1.0
+            found = re.match(r"(.*\.)e\d+\.(gate|up|down)$", name)
+            if found and found.group(1) in used:
+                share = used[found.group(1)]
+            flops += int(2 * tokens * tensor.shape[0] * tensor.shape[1] * share)
     flops += 2 * spec.vocab_size * spec.hidden_size          # one row of logits
     for call in spec.order:
         mixer = spec.layers[call.layer].mixer
@@ -213,7 +226,12 @@ def model_flops(spec, tokens):
         for part in mixers:
             if part.kind == "attention":
                 width = part["heads"] * part["head_dim"]
-                flops += 4 * width * tokens * (tokens + 1) // 2   # causal QK^T and PV
+                window = part.get("window") or tokens
+                seen = sum(min(i + 1, window) for i in range(tokens))
+                flops += 4 * width * seen                       # causal (windowed) QK^T and PV
+            elif part.kind == "lightning":
+                # 32-bit multiply-adds of the recurrence (not tensor-core work, but work)
+                flops += 4 * tokens * part["heads"] * part["key_dim"] * part["value_dim"]
     return flops
 
 
@@ -865,6 +883,229 @@ def case_galarax(args) -> int:
     return 0
 
 
+# --------------------------------------------------------------------------- Farorax beside Galarax
+
+
+def farorax_shape(width: int, layers: int, vocab: int = 65536) -> dict:
+    """A Farorax of the sizes that a model of this width has: one attention layer in four (heads
+    of 64, one key head per four query heads, a window of 1024, the whole head rotated), the
+    others lightning layers with heads of 128 x 128 (inner width = model width); feed-forwards in
+    turn gated of four times the width and eight routed experts of the model's width of which a
+    token uses two, beside a shared one."""
+    attention = {"heads": width // 64, "kv_heads": width // 256, "dim": 64, "vdim": 64,
+                 "scale": 0.125, "mask": {"size": 1024},
+                 "rot": {"base": 1000000.0, "dims": 64, "scaling": {
+                     "factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    heads = width // 128
+    lightning = {"heads": heads, "dim": 128, "vdim": 128,
+                 "decay": [1.0 - 2.0 ** (-3 - 5 * h / max(heads - 1, 1)) for h in range(heads)]}
+    dense = {"kind": "dense", "ff": 4 * width}
+    routed = {"kind": "moe", "expert": {"ff": width}, "shared": {"ff": width},
+              "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    entries = []
+    for index in range(layers):
+        mixer = ("attention", attention) if index % 4 == 0 else ("lightning", lightning)
+        entries.append({"type": mixer[0], "mixer": mixer[1], "mlp": routed if index % 2 else dense})
+    return {"architecture": "Farorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "residual_mult": 0.3, "logit_softcap": 30.0, "layers": entries}
+
+
+def farorax_kernels(width, batch, peak):
+    """The kernels that Farorax adds, alone, beside the like kernels of Galarax, for a decode step
+    of ``batch`` tokens and a prompt of PREFILL_TOKENS tokens: algorithmic bytes (or flops) /
+    time against the measured peaks. Arguments rotate over copies that together exceed L2."""
+    import torch
+
+    from mlx_one_b200.kernels import default_ops
+    from mlx_one_b200.parts import (FixedState, PagedKeyValues, PagedView, StateView,
+                                    StepContext)
+    from mlx_one_b200.parts.mixers import GatedDeltaRule
+
+    ops, device = default_ops("cuda:0"), "cuda:0"
+    ints = lambda values: torch.tensor(values, dtype=torch.int32, device=device)
+    bf16 = lambda *shape: torch.randn(*shape, device=device).bfloat16()
+
+    def ctx_of(portions, histories):
+        positions, owner, starts = [], [], [0]
+        for r, (n, before) in enumerate(zip(portions, histories)):
+            positions += list(range(before, before + n))
+            owner += [r] * n
+            starts.append(starts[-1] + n)
+        return StepContext(tokens=len(positions), requests=len(portions),
+                           token_ids=ints([0] * len(positions)), positions=ints(positions),
+                           token_request=ints(owner), request_start=ints(starts),
+                           history=ints(histories), max_portion=max(portions),
+                           max_context=max(p + h for p, h in zip(portions, histories)))
+
+    def entry(seconds, moved=None, flops=None):
+        out = {"us": round(seconds * 1e6, 2)}
+        if moved is not None:
+            out["gbs"] = round(moved / seconds / 1e9, 1)
+            out["hbm_frac"] = round(moved / seconds / 1e9 / peak["hbm_gbs"], 4)
+        if flops is not None:
+            out["tflops"] = round(flops / seconds / 1e12, 2)
+            out["tensor_frac"] = round(flops / seconds / 1e12 / peak["bf16_tflops"], 4)
+        return out
+
+    H, D, V = width // 128, 128, 128
+    out = {}
+    for label, portions, histories in (("decode", [1] * batch, [2048] * batch),
+                                       ("prefill", [PREFILL_TOKENS], [0])):
+        ctx = ctx_of(portions, histories)
+        tokens, requests = ctx.tokens, ctx.requests
+        # ---- lightning attention beside the gated delta rule, equal heads and sizes
+        state_size = H * D * V
+        copies = max(2, min(24, int(200e6 // (requests * state_size * 4))))
+        state = torch.zeros(copies * requests, state_size, device=device)
+        views = [StateView(state, ints(list(range(c * requests, (c + 1) * requests))),
+                           FixedState((state_size,), "float32")) for c in range(copies)]
+        wide = 2 * H * D + 2 * H * V
+        projected = [bf16(tokens, wide) for _ in range(copies)]
+        decay = torch.full((H,), 0.97, device=device)
+        weight = torch.ones(H * V, device=device)
+        seconds = graph_seconds(lambda i: ops.lightning_attention(
+            projected[i], decay=decay, norm_weight=weight, eps=1e-6, ctx=ctx, view=views[i],
+            write=True, heads=H, key_dim=D, value_dim=V), copies, 2 * copies)
+        moved = tokens * (wide + H * V) * 2 + 2 * requests * state_size * 4
+        out[f"{label}_lightning"] = entry(seconds, moved)
+        out[f"{label}_lightning"]["gflops_fma"] = round(4.0 * tokens * H * D * V / seconds / 1e9, 1)
+        G, taps = width // 256, 4
+        sizes = dict(heads=H, kv_heads=G, key_dim=D, value_dim=V, taps=taps)
+        delta_size = GatedDeltaRule.state_size({"heads": H, "kv_heads": G, "key_dim": D,
+                                                "value_dim": V, "taps": taps})
+        channels = 2 * G * D + H * V
+        delta_wide = channels + H * V + 2 * H
+        delta_state = torch.zeros(copies * requests, delta_size, device=device)
+        delta_views = [StateView(delta_state, views[c].slots, FixedState((delta_size,), "float32"))
+                       for c in range(copies)]
+        delta_in = [bf16(tokens, delta_wide) for _ in range(copies)]
+        constants = dict(conv=torch.randn(channels, taps, device=device) * 0.5,
+                         a_log=torch.zeros(H, device=device), dt_bias=torch.zeros(H, device=device),
+                         norm_weight=torch.ones(V, device=device), eps=1e-6, unit_eps=1e-6,
+                         ctx=ctx, write=True, **sizes)
+        seconds = graph_seconds(lambda i: ops.gated_delta_rule(delta_in[i], view=delta_views[i],
+                                                               **constants), copies, 2 * copies)
+        moved = tokens * (delta_wide + H * V) * 2 + 2 * requests * delta_size * 4
+        out[f"{label}_gated_delta_galarax"] = entry(seconds, moved)
+        del state, views, projected, delta_state, delta_views, delta_in
+        # ---- attention over a window with sinks beside attention without
+        heads, kv_heads, head, window = width // 64, width // 256, 64, 1024
+        pages = -(-(histories[0] + portions[0]) // PAGE_SIZE)
+        table = ints([[r * pages + b for b in range(pages)] for r in range(requests)])
+        kv = (torch.randn(2, requests * pages + 1, kv_heads, PAGE_SIZE, head, device=device) * 0.3).bfloat16()
+        view = PagedView(kv, table, PAGE_SIZE, PagedKeyValues(kv_heads, head, window))
+        q = [bf16(tokens, heads, head) for _ in range(4)]
+        sinks = torch.zeros(heads, device=device)
+        seen = sum(min(h + i + 1, window) for n, h in zip(portions, histories) for i in range(n))
+        moved = requests * min(histories[0] + portions[0], window + portions[0]) * kv_heads * head * 2 * 2 \
+            + tokens * heads * head * 2 * 2
+        flops = 4.0 * heads * head * seen
+        for name, extra in (("attention_sinks", dict(sinks=sinks)), ("attention_plain_galarax", {})):
+            seconds = graph_seconds(lambda i: ops.paged_attention(
+                q[i], heads=heads, kv_heads=kv_heads, head_dim=head, scale=0.125, window=window,
+                ctx=ctx, view=view, **extra), 4, 8)
+            out[f"{label}_{name}"] = entry(seconds, moved, flops)
+        del kv, q
+        # ---- the routed feed-forward beside a gated one of the width a token uses
+        experts, top, ff, shared = 8, 2, width, width
+        copies = max(2, min(12, int(300e6 // ((experts * ff + shared) * width * 6))))
+        stack = experts * ff + shared
+        gate_up = [bf16(2 * stack, width) * 0.02 for _ in range(copies)]
+        down = [bf16(width, stack) * 0.02 for _ in range(copies)]
+        router = torch.randn(experts, width, device=device)
+        x = bf16(tokens, width)
+        routing = dict(experts=experts, top=top, groups=4, keep=2, group_score=2)
+
+        def routed(i):
+            weights = ops.route_experts(x, router, **routing)
+            gated = ops.linear_swiglu(x, gate_up[i])
+            ops.scale_expert_columns(gated, weights, ff)
+            return ops.linear(gated, down[i])
+        used = top * ff + shared
+        seconds = graph_seconds(routed, copies, 2 * copies)
+        touched = min(experts, tokens * top) * ff + shared       # rows of weights a step must read
+        out[f"{label}_routed_ff"] = entry(seconds, touched * width * 6 if label == "decode" else None,
+                                          6.0 * tokens * used * width if label == "prefill" else None)
+        dense_up = [bf16(2 * used, width) * 0.02 for _ in range(copies)]
+        dense_down = [bf16(width, used) * 0.02 for _ in range(copies)]
+        for name, kind in (("gated_ff_gelu", "gelu_tanh"), ("gated_ff_silu_galarax_lfm2", "silu")):
+            seconds = graph_seconds(lambda i: ops.linear(ops.linear_gated(x, dense_up[i], kind),
+                                                         dense_down[i]), copies, 2 * copies)
+            out[f"{label}_{name}"] = entry(seconds, used * width * 6 if label == "decode" else None,
+                                           6.0 * tokens * used * width if label == "prefill" else None)
+        del gate_up, down, dense_up, dense_down
+        # ---- what enters the stream before a pass: the mixing product beside the added vector
+        residual = [torch.zeros(tokens, width, device=device) for _ in range(4)]
+        delta = [bf16(tokens, width) for _ in range(4)]
+        table_e = bf16(4096, width)
+        ids = torch.randint(0, 4096, (tokens,), device=device, dtype=torch.int32)
+        mix = bf16(width, 2 * width) * 0.02
+        vector = torch.zeros(width, device=device)
+
+        def enter(i):
+            both = ops.concat_stream(residual[i], delta[i], ids, table_e, torch.bfloat16, delta_scale=0.3)
+            return ops.linear(both, mix, vector, out_dtype=torch.float32)
+        seconds = graph_seconds(enter, 4, 8)
+        out[f"{label}_loop_entry_mix"] = entry(seconds, tokens * width * (4 + 2 + 2 + 4 + 4) + mix.numel() * 2)
+        seconds = graph_seconds(lambda i: ops.add_vectors(residual[i], delta[i], ids, table_e, vector), 4, 8)
+        out[f"{label}_loop_entry_add_galarax"] = entry(seconds, tokens * width * (4 + 2 + 2 + 4))
+        seconds = graph_seconds(lambda i: ops.add_rmsnorm(residual[i], delta[i], vector, 1e-6,
+                                                          torch.bfloat16, delta_scale=0.3), 4, 8)
+        out[f"{label}_add_rmsnorm_scaled"] = entry(seconds, tokens * width * (4 + 4 + 2 + 2))
+        del residual, delta
+        torch.cuda.empty_cache()
+    return out
+
+
+def case_farorax(args) -> int:
+    """Farorax beside Galarax (the closest of the engine's models: a recurrent mixer with a matrix
+    state beside softmax attention) at equal width, depth and vocabulary, random weights: decode
+    tokens/s at ``--batch`` and ``--context`` (device-timed graph replays of the engine's step),
+    prefill tokens/s of one 2,048-token prompt, each against its bound, and the new kernels alone."""
+    import gc
+
+    import torch
+
+    peak = peaks()
+    warmup, steps = max(args.warmup, 3), min(args.steps, 128)
+    context = args.context or 2048
+    layers = min(args.layers, 8)
+    results = {}
+    for width in (1024, 2048):
+        for label, data in ((f"farorax_w{width}", farorax_shape(width, layers)),
+                            (f"galarax_w{width}", galarax_shape(width, layers))):
+            engine = engine_of(data, args.batch, context, warmup + steps, f"random-{label}")
+            model, spec = engine.model, engine.model.spec
+            weight_bytes = model.weight_bytes()
+            kv_per_token = engine.cache_bytes_per_token()
+            state_bytes = sum(g.storage[:, 0].numel() * g.storage.element_size()
+                              for g in engine.cache.states)
+            seconds, _, mean_context, launches = time_decode(engine, args.batch, context, warmup,
+                                                             steps, seed=3)
+            step_bytes = weight_bytes + args.batch * (mean_context * kv_per_token + 2 * state_bytes)
+            prefill_seconds = time_prefill(engine, PREFILL_TOKENS, 2, 3, seed=5)
+            flops = model_flops(spec, PREFILL_TOKENS)
+            results[label] = {
+                "layers": layers, "weight_mb": round(weight_bytes / 1e6, 1),
+                "state_mb_per_request": round(state_bytes / 1e6, 2),
+                "decode_tokens_per_s": round(args.batch * steps / seconds, 1),
+                "decode_ms_per_step": round(seconds / steps * 1e3, 4),
+                "decode_hbm_frac": round(step_bytes / (seconds / steps) / 1e9 / peak["hbm_gbs"], 4),
+                "launches_per_step": launches,
+                "prefill_tokens_per_s": round(PREFILL_TOKENS / prefill_seconds, 1),
+                "prefill_ms": round(prefill_seconds * 1e3, 3),
+                "prefill_tensor_frac": round(flops / prefill_seconds / (peak["bf16_tflops"] * 1e12), 4)}
+            del engine, model
+            gc.collect()
+            torch.cuda.empty_cache()
+        results[f"kernels_w{width}"] = farorax_kernels(width, args.batch, peak)
+    print(json.dumps({"case": "farorax", "batch": args.batch, "context": context, "steps": steps,
+                      "warmup": warmup, "dtype": "bf16", "peaks": peak["source"],
+                      "data": "synthetic: random weights, seeded uniform-random token ids",
+                      "results": results}))
+    return 0
+
+
 def decode_step_case(batch: int, context: int) -> int:
     """A few eager decode steps of the whole model at the benchmark's sizes, for a list of the
     step's launches (`ncu --metrics gpu__time_duration.sum`): the prompts are fed first, the last
@@ -1183,7 +1424,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=None,
                         help="context length (default 4096; --case long: prompt tokens, 32768)")
-    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long", "galarax"],
+    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long", "galarax", "farorax"],
                         help="decode: the default line; batching: 128 requests batched "
                              "continuously (LFM2-700M shape); long: 4 x 32,768 tokens "
                              "(LFM2-350M shape)")
@@ -1213,6 +1454,8 @@ def main() -> int:
         return case_long(args)
     if args.case == "galarax":
         return case_galarax(args)
+    if args.case == "farorax":
+        return case_farorax(args)
     args.context = args.context or 4096
     if args.kernel:
         return kernel_case(args.kernel, args.batch, args.context)

@@ -265,7 +265,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          int box_keys, const int* __restrict__ request_start,
                          const int* __restrict__ history, bf16* __restrict__ out, int requests,
                          int heads, int kv_heads, float scale_log2, int window, int token_tiles,
-                         int splits, float* __restrict__ partial, int* __restrict__ error_flag) {
+                         int splits, float* __restrict__ partial, const float* __restrict__ sinks,
+                         int* __restrict__ error_flag) {
     using S = Shape<KEYS>;
     constexpr int COPY_WARP = 4 * PARTS, MMA_WARP = 4 * PARTS + 1;
     constexpr int THREADS = (4 * PARTS + 2) * 32;     // softmax warps, the copy warp, the product warp
@@ -653,6 +654,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
                 for (int other = 0; other < PARTS; ++other) l += sums[other * ROWS + row];
             }
+            if (sinks != nullptr && item.split == 0 && valid) {
+                // A sink: a term exp(sink) of the denominator that has no key and no value. It
+                // joins the row's sum at the end, against the maximum that the sum was taken
+                // against (every part holds the same m and, by now, the same l); a row that saw
+                // no key in this split is left with the sink alone. Counted once: by split 0.
+                const float sink = sinks[item.kv_head * group + row % group] * 1.4426950408889634f;
+                if (m == -INFINITY) { m = sink; l = 1.f; }
+                else l += fast_exp2(fminf(sink - m, 126.f));
+            }
             if (ok && valid && split_row != nullptr) {
                 // unnormalised, against m: the merge scales the splits to their common maximum
 #pragma unroll
@@ -751,14 +761,15 @@ MLXONE_API int mlxone_attention_tcgen05_splits(int tokens, int requests, int hea
 
 // q: [tokens, heads, 64] bfloat16; kv: [2, pages, kv_heads, page_size, 64]; out: [tokens, heads * 64].
 // splits > 1 (with partial, see mlxone_attention_tcgen05_splits): the items are cut by keys and
-// `out` is left for the merge to write.
+// `out` is left for the merge to write. `sinks` (float32 [heads] or null): exp(sink) of a query's
+// head stands in the denominator of its softmax beside the keys' terms.
 MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, const int* block_table,
                                                 int table_width, int page_size, int pages,
                                                 const int* request_start, const int* history,
                                                 void* out, int tokens, int requests, int heads,
                                                 int kv_heads, int head_dim, float scale, int window,
-                                                int splits, float* partial, int* error_flag,
-                                                cudaStream_t stream) {
+                                                int splits, float* partial, const float* sinks,
+                                                int* error_flag, cudaStream_t stream) {
     if (tokens == 0) return 0;
     MLXONE_REQUIRE(tokens > 0 && requests > 0, "attention_prefill_tcgen05: bad sizes");
     MLXONE_REQUIRE(supported(head_dim, heads, kv_heads, page_size),
@@ -836,7 +847,7 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
     kernel<<<dim3((unsigned)blocks), threads, shared, stream>>>(
         map_q, map_kv, value_rows, block_table, table_width, page_size, box_keys, request_start,
         history, static_cast<bf16*>(out), requests, heads, kv_heads, scale * 1.4426950408889634f,
-        window, token_tiles, splits, partial, error_flag);
+        window, token_tiles, splits, partial, sinks, error_flag);
     MLXONE_LAUNCH_CHECK("attention_prefill_tcgen05");
     return 0;
 }

@@ -146,7 +146,13 @@ __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     const __grid_constant__ CUtensorMap map_w, const float* __restrict__ bias,
                     void* out, int ldo, int m, int n, int k, int up_offset, int tiles_m,
-                    int total_tiles, int* __restrict__ error_flag) {
+                    int total_tiles, int* __restrict__ error_flag,
+                    const int2* __restrict__ groups, int out_limit) {
+    // `groups` (null: one product): per tile of 128 rows of `a`, where its rows' weights lie in
+    // `w` (x: first row, or -1 for a tile without rows, which is left out; y: first column).
+    // Rows of `a` sorted by expert, each expert's rows padded to whole tiles, and the experts'
+    // matrices stacked in `w`: a product per expert in one launch. `out_limit` is the number of
+    // output columns (the width of one expert's result).
     constexpr int A_BYTES = BM * BK * 2, W_BYTES = BN * BK * 2;
     constexpr int OUT_COLUMNS = EPILOGUE == SWIGLU ? BN / 2 : BN;
     extern __shared__ unsigned char shared_raw[];
@@ -189,7 +195,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 const int tile_m = (tile % tiles_m) * BM;
-                const int tile_n = (tile / tiles_m) * OUT_COLUMNS;
+                int tile_n = (tile / tiles_m) * OUT_COLUMNS, w_column = 0;
+                if (groups != nullptr) {
+                    const int2 group = groups[tile % tiles_m];
+                    if (group.x < 0) continue;
+                    tile_n += group.x;
+                    w_column = group.y;
+                }
                 for (int kt = 0; kt < k_tiles; ++kt, ++step) {
                     const int s = step % STAGES;
                     ok = barrier_wait(empty(s), ((step / STAGES) & 1) ^ 1, error_flag);
@@ -197,9 +209,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     barrier_expect(full(s), A_BYTES + W_BYTES);
                     const uint32_t a_tile = tiles + s * (A_BYTES + W_BYTES);
                     tma_load_2d(a_tile, &map_a, kt * BK, tile_m, full(s));
-                    tma_load_2d(a_tile + A_BYTES, &map_w, kt * BK, tile_n, full(s));
+                    tma_load_2d(a_tile + A_BYTES, &map_w, w_column + kt * BK, tile_n, full(s));
                     if (EPILOGUE == SWIGLU)
-                        tma_load_2d(a_tile + A_BYTES + W_BYTES / 2, &map_w, kt * BK,
+                        tma_load_2d(a_tile + A_BYTES + W_BYTES / 2, &map_w, w_column + kt * BK,
                                     up_offset + tile_n, full(s));
                 }
             }
@@ -209,7 +221,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             constexpr uint32_t idesc = instruction_descriptor(BM, BN);
             int step = 0, round = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++round) {
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (groups != nullptr && groups[tile % tiles_m].x < 0) continue;
                 const int buffer = round & 1;
                 // the epilogue must have read this buffer's previous tile
                 ok = barrier_wait(drained(buffer), ((round >> 1) & 1) ^ 1, error_flag);
@@ -231,6 +244,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                     mma_commit(empty(s));                  // the stage is free once these finish
                 }
                 if (ok) mma_commit(ready(buffer));
+                ++round;
             }
         }
     } else {
@@ -239,18 +253,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const int quarter = warp & 3;
         float* turn = reinterpret_cast<float*>(shared_raw + (tiles - shared_address(shared_raw)) +
                                                STAGES * (A_BYTES + W_BYTES)) + (warp - 2) * 32 * 33;
-        const int limit = EPILOGUE == SWIGLU ? up_offset : n;
+        const int limit = out_limit;
         // whether every row of the output starts on a 16-byte boundary
         const bool whole_rows =
             (EPILOGUE == STORE_BF16 || EPILOGUE == SWIGLU)
                 ? (ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
                 : (ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0);
         int round = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
-            const int buffer = round & 1;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            if (groups != nullptr && groups[tile % tiles_m].x < 0) continue;
+            const int buffer = round++ & 1;
             const int tile_m = (tile % tiles_m) * BM;
             const int tile_n = (tile / tiles_m) * OUT_COLUMNS;
-            if (!barrier_wait(ready(buffer), (round >> 1) & 1, error_flag)) break;
+            if (!barrier_wait(ready(buffer), ((round - 1) >> 1) & 1, error_flag)) break;
             fence_after_sync();
             const uint32_t accumulator = tmem_base + buffer * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
@@ -405,17 +420,30 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long colu
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// What a grouped product adds: the stacked matrix's own extent ([w_rows, w_columns], row stride
+// w_ld), the tiles' places in it, and the width of one group's result.
+struct Grouping {
+    const int2* groups = nullptr;
+    long long w_rows = 0, w_columns = 0, w_ld = 0;
+    int out_limit = 0;
+};
+
 template <int BN, int EPILOGUE, int STAGES>
 int launch(const void* a, int lda, const void* w, const float* bias, void* out, int ldo, int m,
-           int n, int k, int up_offset, int* error_flag, cudaStream_t stream) {
+           int n, int k, int up_offset, int* error_flag, cudaStream_t stream,
+           Grouping grouping = Grouping()) {
     CUtensorMap map_a, map_w;
     const int w_box = EPILOGUE == SWIGLU ? BN / 2 : BN;
-    if (!make_map(&map_a, a, m, k, lda, BM) || !make_map(&map_w, w, n, k, k, w_box)) {
+    const bool grouped = grouping.groups != nullptr;
+    const bool mapped = grouped
+        ? make_map(&map_w, w, grouping.w_rows, grouping.w_columns, grouping.w_ld, w_box)
+        : make_map(&map_w, w, n, k, k, w_box);
+    if (!make_map(&map_a, a, m, k, lda, BM) || !mapped) {
         mlxone_set_error("gemm_tcgen05: cannot encode a tensor map");
         return 2;
     }
     const int out_columns = EPILOGUE == SWIGLU ? BN / 2 : BN;
-    const int columns = EPILOGUE == SWIGLU ? up_offset : n;
+    const int columns = grouped ? grouping.out_limit : EPILOGUE == SWIGLU ? up_offset : n;
     const int tiles_m = (m + BM - 1) / BM;
     const int total_tiles = tiles_m * ((columns + out_columns - 1) / out_columns);
     if (g_sm_count == 0) {
@@ -434,7 +462,8 @@ int launch(const void* a, int lda, const void* w, const float* bias, void* out, 
         return 2;
     }
     kernel<<<grid, THREADS, shared, stream>>>(map_a, map_w, bias, out, ldo, m, n, k, up_offset,
-                                              tiles_m, total_tiles, error_flag);
+                                              tiles_m, total_tiles, error_flag, grouping.groups,
+                                              columns);
     return 0;
 }
 
@@ -482,5 +511,46 @@ MLXONE_API int mlxone_gemm_tcgen05(const void* a, int lda, const void* w, const 
     }
     if (code != 0) return code;
     MLXONE_LAUNCH_CHECK("gemm_tcgen05");
+    return 0;
+}
+
+// One product per group of rows in one launch. a: [m, k] (row stride lda), its rows sorted by
+// group and every group's rows padded to whole tiles of 128; groups: int32 [m / 128, 2], per
+// tile the first row and the first column of its group's matrix inside the stacked w
+// [w_rows, w_columns] (row stride w_ld), or -1 for a tile without rows. epilogue 0: out bf16
+// [m, n] = a_tile w_group^T with w_group [n, k]; epilogue 1 (SwiGLU): w_group's n gate rows start
+// at the tile's row, its up rows `up_offset` rows further, out bf16 [m, n].
+MLXONE_API int mlxone_gemm_tcgen05_grouped(const void* a, int lda, const void* w, long long w_rows,
+                                           long long w_columns, long long w_ld, void* out, int ldo,
+                                           int m, int n, int k, int up_offset, int epilogue,
+                                           const int* groups, int* error_flag,
+                                           cudaStream_t stream) {
+    if (m == 0 || n == 0) return 0;
+    MLXONE_REQUIRE(find_encoder(), "gemm_tcgen05: the driver has no cuTensorMapEncodeTiled");
+    MLXONE_REQUIRE(m > 0 && m % BM == 0 && n > 0 && k > 0 && k % 8 == 0 && lda % 8 == 0 &&
+                       w_ld % 8 == 0,
+                   "gemm_tcgen05_grouped: whole tiles of rows, and K (%d) and the row strides "
+                   "(%d, %lld) multiples of 8", k, lda, w_ld);
+    MLXONE_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(w) & 15) == 0 && groups != nullptr,
+                   "gemm_tcgen05_grouped: operands must be 16-byte aligned");
+    MLXONE_REQUIRE(epilogue == STORE_BF16 || epilogue == SWIGLU,
+                   "gemm_tcgen05_grouped: epilogue %d is not built", epilogue);
+    Grouping grouping;
+    grouping.groups = reinterpret_cast<const int2*>(groups);
+    grouping.w_rows = w_rows; grouping.w_columns = w_columns; grouping.w_ld = w_ld;
+    grouping.out_limit = n;
+    int code;
+    if (epilogue == SWIGLU)
+        code = launch<256, SWIGLU, WIDE_STAGES>(a, lda, w, nullptr, out, ldo, m, n, k, up_offset,
+                                                error_flag, stream, grouping);
+    else if (n > 128)
+        code = launch<256, STORE_BF16, WIDE_STAGES>(a, lda, w, nullptr, out, ldo, m, n, k, 0,
+                                                    error_flag, stream, grouping);
+    else
+        code = launch<128, STORE_BF16, NARROW_STAGES>(a, lda, w, nullptr, out, ldo, m, n, k, 0,
+                                                      error_flag, stream, grouping);
+    if (code != 0) return code;
+    MLXONE_LAUNCH_CHECK("gemm_tcgen05_grouped");
     return 0;
 }

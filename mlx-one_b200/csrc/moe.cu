@@ -109,7 +109,129 @@ __global__ void scale_expert_columns_kernel(T* __restrict__ x, int ld, const flo
     *at = from_float<T>(to_float<T>(*at) * w);
 }
 
+// ------------------------------------------------------------------ tokens sorted by expert
+// For the grouped products: every (token, chosen expert) pair gets a row in a buffer in which
+// each expert's rows lie together and start on a multiple of 128 rows. One block.
+//   pair_row[t, e]  the pair's row (-1: e was not chosen for t)
+//   groups[tile]            {first row, first column} of the tile's expert in the stacked matrix
+//                           of the first product: {expert * width, 0}; {-1, -1}: no rows
+//   groups[tiles + tile]    the same for the second product: {0, expert * width}
+// The order of an expert's rows is whatever the atomics make of it: a row's result does not
+// depend on where it lies.
+constexpr int SORT_THREADS = 1024;
+
+__global__ void __launch_bounds__(SORT_THREADS)
+sort_by_expert_kernel(const float* __restrict__ weights, int* __restrict__ pair_row,
+                      int2* __restrict__ groups, int tokens, int experts, int width, int tiles) {
+    __shared__ int count[MAX_EXPERTS];
+    __shared__ int start[MAX_EXPERTS];
+    griddep_launch();
+    griddep_wait();
+    for (int e = threadIdx.x; e < experts; e += SORT_THREADS) count[e] = 0;
+    __syncthreads();
+    const long long pairs = (long long)tokens * experts;
+    for (long long i = threadIdx.x; i < pairs; i += SORT_THREADS)
+        pair_row[i] = weights[i] > 0.f ? atomicAdd(&count[i % experts], 1) : -1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int e = 0; e < experts; ++e) {
+            start[e] = tile * 128;
+            const int its = (count[e] + 127) / 128;
+            for (int i = 0; i < its && tile < tiles; ++i, ++tile) {
+                groups[tile] = make_int2(e * width, 0);
+                groups[tiles + tile] = make_int2(0, e * width);
+            }
+        }
+        for (; tile < tiles; ++tile) groups[tile] = groups[tiles + tile] = make_int2(-1, -1);
+    }
+    __syncthreads();
+    for (long long i = threadIdx.x; i < pairs; i += SORT_THREADS)
+        if (pair_row[i] >= 0) pair_row[i] += start[i % experts];
+}
+
+// sorted[pair_row[t, e], :] = x[t, :] for every chosen pair. One block per token.
+template <typename T>
+__global__ void gather_by_expert_kernel(const T* __restrict__ x, int ld, const int* __restrict__ pair_row,
+                                        T* __restrict__ sorted, int hidden, int experts) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    for (int e = 0; e < experts; ++e) {
+        const int row = pair_row[(size_t)t * experts + e];
+        if (row < 0) continue;
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+            sorted[(size_t)row * hidden + c] = x[(size_t)t * ld + c];
+    }
+}
+
+// out[t, :] = sum over chosen e of weights[t, e] * y[pair_row[t, e], :] (+ shared[t, :]), in
+// 32-bit, experts in ascending order.
+template <typename T>
+__global__ void combine_experts_kernel(const T* __restrict__ y, const int* __restrict__ pair_row,
+                                       const float* __restrict__ weights, const T* __restrict__ shared_out,
+                                       T* __restrict__ out, int hidden, int experts) {
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float sum = shared_out != nullptr ? to_float<T>(shared_out[(size_t)t * hidden + c]) : 0.f;
+        for (int e = 0; e < experts; ++e) {
+            const int row = pair_row[(size_t)t * experts + e];
+            if (row >= 0)
+                sum = fmaf(weights[(size_t)t * experts + e], to_float<T>(y[(size_t)row * hidden + c]), sum);
+        }
+        out[(size_t)t * hidden + c] = from_float<T>(sum);
+    }
+}
+
 }  // namespace
+
+MLXONE_API int mlxone_sort_by_expert(const float* weights, int* pair_row, int* groups, int tokens,
+                                     int experts, int width, int tiles, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && experts > 0 && experts <= MAX_EXPERTS && tiles > 0,
+                   "sort_by_expert: bad sizes");
+    launch_kernel(sort_by_expert_kernel, dim3(1), dim3(SORT_THREADS), 0, stream, true, weights,
+                  pair_row, reinterpret_cast<int2*>(groups), tokens, experts, width, tiles);
+    MLXONE_LAUNCH_CHECK("sort_by_expert");
+    return 0;
+}
+
+MLXONE_API int mlxone_gather_by_expert(const void* x, int ld, const int* pair_row, void* sorted,
+                                       int tokens, int hidden, int experts, int dtype,
+                                       cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && hidden > 0 && experts > 0, "gather_by_expert: bad sizes");
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == MLXONE_BF16)
+        launch_kernel(gather_by_expert_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
+                      true, (const __nv_bfloat16*)x, ld, pair_row, (__nv_bfloat16*)sorted, hidden,
+                      experts);
+    else
+        launch_kernel(gather_by_expert_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true,
+                      (const float*)x, ld, pair_row, (float*)sorted, hidden, experts);
+    MLXONE_LAUNCH_CHECK("gather_by_expert");
+    return 0;
+}
+
+MLXONE_API int mlxone_combine_experts(const void* y, const int* pair_row, const float* weights,
+                                      const void* shared_out, void* out, int tokens, int hidden,
+                                      int experts, int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && hidden > 0 && experts > 0, "combine_experts: bad sizes");
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == MLXONE_BF16)
+        launch_kernel(combine_experts_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
+                      true, (const __nv_bfloat16*)y, pair_row, weights,
+                      (const __nv_bfloat16*)shared_out, (__nv_bfloat16*)out, hidden, experts);
+    else
+        launch_kernel(combine_experts_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true,
+                      (const float*)y, pair_row, weights, (const float*)shared_out, (float*)out,
+                      hidden, experts);
+    MLXONE_LAUNCH_CHECK("combine_experts");
+    return 0;
+}
 
 MLXONE_API int mlxone_route_experts(const void* x, int ld, const float* router, float* weights,
                                     int tokens, int hidden, int experts, int top, int groups,

@@ -533,6 +533,59 @@ class CudaOps:
                    _c_void_p(_ptr(weights)), _c_int(gated.shape[0]), _c_int(weights.shape[1]),
                    _c_int(width), _c_int(_dtype_code(gated.dtype)))
 
+    # Steps of at least this many tokens run routed experts over tokens sorted by expert (grouped
+    # tcgen05 products that touch only the experts a token uses); smaller steps run every token
+    # through all experts in one stacked product, which reads the same weights at those sizes.
+    sorted_experts_min_tokens = 128
+
+    def sorts_experts(self, x, *, experts, width, top, stack) -> bool:
+        """Whether ``routed_experts_sorted`` takes this step."""
+        return (self.tcgen05_products and x.dtype == torch.bfloat16 and top < experts
+                and x.shape[0] >= self.sorted_experts_min_tokens
+                and x.shape[1] % 8 == 0 and width % 8 == 0 and stack % 8 == 0
+                and x.stride(1) == 1 and x.stride(0) % 8 == 0)
+
+    def routed_experts_sorted(self, x, weights, gate_up, down, *, experts, width, top,
+                              shared_gate_up=None, shared_down=None):
+        """The weighted sum of every token's chosen experts (+ the shared expert's output), with
+        the tokens sorted by expert: gate_up [2 stack, hidden] holds the experts' gate rows, then
+        (``stack`` rows further) their up rows; down [hidden, stack] their down matrices side by
+        side. weights [tokens, experts] float32, zero where an expert was not chosen."""
+        tokens, hidden = x.shape
+        stack = gate_up.shape[0] // 2
+        tiles = -(-(tokens * top + experts * 127) // 128)
+        rows = tiles * 128
+        pair_row = torch.empty((tokens, experts), dtype=torch.int32, device=self.device)
+        groups = torch.empty((2, tiles, 2), dtype=torch.int32, device=self.device)
+        self._call("mlxone_sort_by_expert", _c_void_p(_ptr(weights)), _c_void_p(_ptr(pair_row)),
+                   _c_void_p(_ptr(groups)), _c_int(tokens), _c_int(experts), _c_int(width),
+                   _c_int(tiles))
+        # (rows that no pair owns are never read back; zeros keep their products finite)
+        sorted_x = torch.zeros((rows, hidden), dtype=x.dtype, device=self.device)
+        self._call("mlxone_gather_by_expert", _c_void_p(_ptr(x)), _c_int(x.stride(0)),
+                   _c_void_p(_ptr(pair_row)), _c_void_p(_ptr(sorted_x)), _c_int(tokens),
+                   _c_int(hidden), _c_int(experts), _c_int(_dtype_code(x.dtype)))
+        gated = torch.empty((rows, width), dtype=x.dtype, device=self.device)
+        self._call("mlxone_gemm_tcgen05_grouped", _c_void_p(_ptr(sorted_x)), _c_int(hidden),
+                   _c_void_p(_ptr(gate_up)), _c_ll(gate_up.shape[0]), _c_ll(hidden), _c_ll(hidden),
+                   _c_void_p(_ptr(gated)), _c_int(width), _c_int(rows), _c_int(width),
+                   _c_int(hidden), _c_int(stack), _c_int(self._SWIGLU),
+                   _c_void_p(_ptr(groups[0])), _c_void_p(_ptr(self.error_flag)))
+        y = torch.empty((rows, hidden), dtype=x.dtype, device=self.device)
+        self._call("mlxone_gemm_tcgen05_grouped", _c_void_p(_ptr(gated)), _c_int(width),
+                   _c_void_p(_ptr(down)), _c_ll(hidden), _c_ll(stack), _c_ll(stack),
+                   _c_void_p(_ptr(y)), _c_int(hidden), _c_int(rows), _c_int(hidden), _c_int(width),
+                   _c_int(0), _c_int(self._STORE), _c_void_p(_ptr(groups[1])),
+                   _c_void_p(_ptr(self.error_flag)))
+        shared_out = None
+        if shared_gate_up is not None:
+            shared_out = self.linear(self.linear_swiglu(x, shared_gate_up), shared_down)
+        out = torch.empty((tokens, hidden), dtype=x.dtype, device=self.device)
+        self._call("mlxone_combine_experts", _c_void_p(_ptr(y)), _c_void_p(_ptr(pair_row)),
+                   _c_void_p(_ptr(weights)), _c_void_p(_ptr(shared_out)), _c_void_p(_ptr(out)),
+                   _c_int(tokens), _c_int(hidden), _c_int(experts), _c_int(_dtype_code(x.dtype)))
+        return out
+
     # ---- lightning attention
 
     def lightning_attention(self, projected, *, decay, norm_weight, eps, ctx, view, write, heads,
@@ -827,7 +880,7 @@ class CudaOps:
             rest = ctx.requests - singles
             table = view.block_table[singles:]
             starts, history = ctx.request_start[singles:], ctx.history[singles:]
-            if (self.tcgen05_attention and q.dtype == torch.bfloat16 and sinks is None
+            if (self.tcgen05_attention and q.dtype == torch.bfloat16
                     and self.lib.mlxone_attention_tcgen05_supports(
                         _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):
                 # few query tiles (a prompt's portion beside a step's decodes): their keys are
@@ -851,7 +904,7 @@ class CudaOps:
                            _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
                            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
                            _c_int(window or 0), _c_int(splits), _c_void_p(_ptr(partial)),
-                           _c_void_p(_ptr(self.error_flag)))
+                           _c_void_p(_ptr(sinks)), _c_void_p(_ptr(self.error_flag)))
                 if partial is not None:
                     # (the leading single tokens are the decode kernel's: their rows stay)
                     skip = singles * heads * splits * (head_dim + 2)

@@ -95,11 +95,12 @@ class RoutedExperts(FeedForward):
     expert's, which every token uses with weight 1.
 
     The experts' gate and up matrices are stacked into one matrix and their down matrices side
-    by side into another (the shared expert last). ``dense`` execution runs every token through
-    all of it: one product with the gate, the routing weights multiplied into the expert's
-    columns (zero for experts that were not chosen), one down product. ``sorted`` execution
-    (the kernels' grouped products over tokens sorted by expert) is used where the kernel set
-    offers it and it is cheaper."""
+    by side into another (the shared expert last). Small steps run every token through all of
+    it: one product with the gate, the routing weights multiplied into the expert's columns
+    (zero for experts that were not chosen), one down product; at those sizes every expert's
+    weights are read anyway. Where the kernel set offers it (``sorts_experts``) larger steps sort
+    their (token, expert) pairs by expert and run one grouped product per matrix over the same
+    stacked weights, so that a token costs only the experts it uses."""
 
     @classmethod
     def tensors(cls, spec):
@@ -132,12 +133,25 @@ class RoutedExperts(FeedForward):
                                              [tensors[name + "up"] for name in names], dim=0))
         self.down = self.matrix(torch.cat([tensors[name + "down"] for name in names], dim=1))
         self.router = tensors["router"].to(torch.float32).contiguous()
+        # the shared expert once more on its own, for steps that sort their tokens by expert
+        self.shared = {}
+        self.sortable = self.activation == "silu" and hasattr(self.ops, "sorts_experts")
+        if self.sortable and self.shared_width:
+            self.shared = dict(
+                shared_gate_up=self.matrix(torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0)),
+                shared_down=self.matrix(tensors["shared.down"]))
 
     fuses_residual = True
     scales_residual = True
 
     def forward(self, x, ctx, residual=None):
         weights = self.ops.route_experts(x, self.router, **self.routing)
+        if self.sortable and self.ops.sorts_experts(x, experts=self.experts, width=self.width,
+                                                    top=self.routing["top"],
+                                                    stack=self.gate_up.shape[0] // 2):
+            return self.ops.routed_experts_sorted(
+                x, weights, self.gate_up, self.down, experts=self.experts, width=self.width,
+                top=self.routing["top"], **self.shared)
         if self.activation == "silu":
             gated = self.ops.linear_swiglu(x, self.gate_up)
         else:

@@ -90,7 +90,7 @@ F3 = {"architecture": "Farorax", "vocab": 512, "width": 128, "norm": {"eps": 2e-
 F4 = {"architecture": "Farorax", "vocab": 64, "width": 32, "norm": {"eps": 1e-5},
       "residual_mult": 1.5,
       "layers": [attention(1, 1, 8, 8, 0.5, 1, {"base": 100.0, "dims": 2}, dense(48)),
-                 lightning(1, 4, 4, (0.5,), None)],
+                 lightning(1, 4, 12, (0.5,), None)],
       "loop": {"start": 0, "stop": 2, "times": 1}}
 
 # sizes that are multiples of nothing much: width 72, vocabulary 100, three query heads on one
@@ -106,7 +106,18 @@ F5 = {"architecture": "Farorax", "vocab": 100, "width": 72, "norm": {"eps": 3e-6
           attention(2, 2, 40, 24, 0.15, 200, None, None)],
       "loop": {"start": 1, "stop": 3, "times": 2}}
 
-CONFIGS = {"F1": (F1, 21, 4), "F2": (F2, 22, 8), "F3": (F3, 23, 16), "F4": (F4, 24, 2),
+# no routed experts (in bfloat16 nothing is decided by a hair, so every row is held to the
+# bound): heads of 64 in pairs on a key head with a window of 40, lightning keys of 64, a loop over
+# the last two layers
+F6 = {"architecture": "Farorax", "vocab": 384, "width": 128, "norm": {"eps": 1e-5},
+      "residual_mult": 0.4, "logit_softcap": 12.0,
+      "layers": [
+          lightning(2, 64, 64, (0.98, 0.8), dense(192)),
+          attention(4, 2, 64, 64, 0.125, 40, {"base": 8000.0, "dims": 64}, dense(192)),
+          lightning(4, 32, 32, (0.99, 0.9, 0.7, 0.5), None)],
+      "loop": {"start": 1, "stop": 3, "times": 2}}
+
+CONFIGS = {"F6": (F6, 26, 16), "F1": (F1, 21, 4), "F2": (F2, 22, 8), "F3": (F3, 23, 16), "F4": (F4, 24, 2),
            "F5": (F5, 25, 8)}   # config, seed, page
 
 
@@ -155,17 +166,21 @@ def make_model_dir(name: str, root: Path | None = None, config: dict | None = No
 # bfloat16: a row's error is the root mean square over the vocabulary of (engine - plain), its
 # mean taken off, relative to the spread of the plain logits. Rounding alone gives a few percent
 # on these models; a wrong key, a lost state or a token fed twice gives 15 % and more.
-BF16_ROW_ERROR = 0.08
+BF16_ROW_ERROR = 0.12
 USUAL_NOISE = 5e-6
-# A position whose routing margin is below this is decided by rounding in bfloat16 (the engine
-# routes the bfloat16 rounding of the normed stream): such rows are not compared in bfloat16.
-ROUTING_MARGIN = 0.01
+# The bfloat16 engine routes what its own 16-bit arithmetic has made of the stream (about a
+# percent from the plain model's), so a position whose routing margin is below this may go to
+# other experts than in the plain model; its own logits are then others, and so, a little, are
+# those of every later position of the request (the layers after it carry it on). Rows from the
+# first such position on are held to the looser rule below.
+ROUTING_MARGIN = 0.05
 
 
 def assert_rows_close(got: torch.Tensor, want: torch.Tensor, dtype, what: str = "") -> None:
     """float32: every logit within 1e-4 + 1e-4 |plain| + 4 x the position's noise (positions with
     a routing margin below 1e-5 left out). bfloat16: every row's error (see above) within
-    ``BF16_ROW_ERROR``, positions with a small routing margin left out, which must be few."""
+    ``BF16_ROW_ERROR`` up to the first position that is routed by a hair; of the rows from there
+    on, two in three."""
     noise, margin = getattr(want, "noise", None), getattr(want, "margin", None)
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, f"{what}: {tuple(got.shape)} against {tuple(want.shape)}"
@@ -182,9 +197,17 @@ def assert_rows_close(got: torch.Tensor, want: torch.Tensor, dtype, what: str = 
     spread = (want - want.mean(-1, keepdim=True)).pow(2).mean().sqrt()
     rows = difference.pow(2).mean(-1).sqrt() / spread
     allowed = BF16_ROW_ERROR * torch.clamp(noise / USUAL_NOISE, min=1.0)
-    compared = margin >= ROUTING_MARGIN
-    assert compared.float().mean() >= 0.5 or want.shape[0] < 8, \
-        f"{what}: most positions of this request are routed by a hair; choose other weights"
-    bad = (rows > allowed) & compared
-    assert not bad.any(), (f"{what}: row error {rows[compared].max():.3f} of the spread; rows "
+    settled = torch.cumsum((margin < ROUTING_MARGIN).float(), 0) == 0
+    bad = (rows > allowed) & settled
+    assert not bad.any(), (f"{what}: row error {rows[settled].max():.3f} of the spread; rows "
                            f"{torch.nonzero(bad).flatten().tolist()[:8]}")
+    if (~settled).any():
+        within = (rows[~settled] <= allowed[~settled]).float().mean()
+        assert within >= 0.66, f"{what}: only {within:.2f} of the rows behind a close routing agree"
+
+
+def sliced(want: torch.Tensor, count: int) -> torch.Tensor:
+    """The first ``count`` rows of a plain model's logits, with their noise and margins."""
+    out = want[:count]
+    out.noise, out.margin = want.noise[:count], want.margin[:count]
+    return out

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from farorax_models import (CONFIGS, F1, assert_rows_close as assert_close, attention, dense,
-                            lightning, make_model_dir)
+                            lightning, make_model_dir, sliced)
 from plain_farorax import (PlainModel, decayed_outer_product_state, gelu_tanh, pair_frequencies,
                            rms_norm, rotate_neighbours, routing, silu, windowed_attention_with_sink)
 from tiny_models import cut, mixed_schedule, prompts, replay
@@ -147,7 +147,7 @@ def test_window_edges_and_sinks_in_prompts_and_decoding(ops, dtype, heads, kv_he
     # the sink takes its share: without it the output is another
     without = windowed_attention_with_sink(round_trip(q), round_trip(k), round_trip(v), scale,
                                            window, torch.full((heads,), -1e9).double()).reshape(T, -1)
-    assert (without - want).abs().max() > 10 * tolerance
+    assert (without - want).abs().max() > 0.1
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -316,6 +316,41 @@ def test_experts_as_columns_of_one_product(ops, dtype):
     assert torch.equal(got.cpu()[:, experts * width:], gated[:, experts * width:])
 
 
+@pytest.mark.parametrize("tokens, hidden, experts, width, top, shared", [
+    (300, 128, 6, 72, 2, 40), (1000, 256, 8, 256, 3, None), (129, 64, 16, 8, 1, 8),
+    (2048, 192, 4, 136, 3, 136)])
+def test_experts_over_sorted_tokens(ops, tokens, hidden, experts, width, top, shared):
+    """Large steps in bfloat16: tokens sorted by expert and one grouped product per matrix over
+    the stacked weights, against every expert applied to its tokens one by one. Some experts get
+    no token at all, others more than a tile."""
+    generator = torch.Generator().manual_seed(tokens + experts)
+    x = torch.randn(tokens, hidden, generator=generator).bfloat16()
+    stack = experts * width + (shared or 0)
+    gate_up = (torch.randn(2 * stack, hidden, generator=generator) / hidden ** 0.5).bfloat16()
+    down = (torch.randn(hidden, stack, generator=generator) / width ** 0.5).bfloat16()
+    weights = torch.zeros(tokens, experts)
+    busy = max(experts - 2, top)                          # the last experts are never chosen
+    for t in range(tokens):
+        chosen = torch.randperm(busy, generator=generator)[:top]
+        weights[t, chosen] = torch.rand(top, generator=generator) + 0.1
+    assert ops.sorts_experts(on(x), experts=experts, width=width, top=top, stack=stack)
+    extra = {}
+    if shared:
+        at = experts * width
+        extra = dict(shared_gate_up=on(torch.cat([gate_up[at:at + shared],
+                                                  gate_up[stack + at:stack + at + shared]])),
+                     shared_down=on(down[:, at:].contiguous()))
+    got = ops.routed_experts_sorted(on(x), on(weights), on(gate_up), on(down), experts=experts,
+                                    width=width, top=top, **extra).cpu().double()
+    ops.check_errors()
+    both = x.double() @ gate_up.double().T
+    gated = (silu(both[:, :stack]) * both[:, stack:]).bfloat16().double()
+    scale = torch.ones(tokens, stack, dtype=torch.float64)
+    scale[:, :experts * width] = weights.double().repeat_interleave(width, dim=1)
+    want = (gated * scale) @ down.double().T
+    assert (got - want).abs().max() < 0.03 * want.abs().max()
+
+
 # ------------------------------------------------------------------ the stream's operations
 
 
@@ -391,7 +426,8 @@ def test_the_stream_after_every_layer(folders, plain):
         if place < 0:
             return
         scale = model.layers[model.order[place].layer].pending_scale
-        seen.append((residual if delta is None else residual + scale * delta.float()).cpu())
+        # (a step's rows may be followed by fillers that round its shape up)
+        seen.append((residual if delta is None else residual + scale * delta.float())[:len(tokens)].cpu())
     model.observer = watch
     replay(runner, cache, [([("r", tokens)], ["r"])])
     model.observer = None
@@ -416,10 +452,7 @@ def test_prefill_against_token_by_token(folders, plain, name, dtype):
     assert_close(replay(runner, cache, steps)["r"], want, dtype, f"{name} prompt then decode")
     steps = [([("s", [t])], []) for t in tokens[:50]]
     steps[-1] = (steps[-1][0], ["s"])
-    got = replay(runner, cache, steps)["s"]
-    expect = want[:50]
-    expect.noise, expect.margin = want.noise[:50], want.margin[:50]
-    assert_close(got, expect, dtype, f"{name} token by token")
+    assert_close(replay(runner, cache, steps)["s"], sliced(want, 50), dtype, f"{name} token by token")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
