@@ -1016,8 +1016,16 @@ def farorax_kernels(width, batch, peak):
         x = bf16(tokens, width)
         routing = dict(experts=experts, top=top, groups=4, keep=2, group_score=2)
 
-        def routed(i):
+        at = experts * ff
+        alone = [(torch.cat([g[at:at + shared], g[stack + at:stack + at + shared]]).contiguous(),
+                  d[:, at:].contiguous()) for g, d in zip(gate_up, down)]
+
+        def routed(i):                  # what the routed feed-forward part runs
             weights = ops.route_experts(x, router, **routing)
+            if ops.sorts_experts(x, experts=experts, width=ff, top=top, stack=stack):
+                return ops.routed_experts_sorted(x, weights, gate_up[i], down[i], experts=experts,
+                                                 width=ff, top=top, shared_gate_up=alone[i][0],
+                                                 shared_down=alone[i][1])
             gated = ops.linear_swiglu(x, gate_up[i])
             ops.scale_expert_columns(gated, weights, ff)
             return ops.linear(gated, down[i])
@@ -1330,6 +1338,26 @@ def kernel_case(name: str, batch: int, context: int) -> int:
                          ctx=ctx, write=True, **sizes)
         run = lambda i: ops.gated_delta_rule(rows[i % 4], view=views[i % 4], **constants)
         work = f"{ctx.tokens} tokens of {len(portions)} requests, 16 heads of 128 x 128, state {slot * 4 / 1e6:.1f} MB a request"
+    elif name in ("lightning_prefill", "lightning_decode"):
+        # lightning attention at the shape of a 2048-wide model: one 2,048-token prompt (segments:
+        # build, chain, scan, then the norm and gate) or `batch` single tokens (scan, norm and gate)
+        from mlx_one_b200.parts import FixedState, StateView
+
+        heads, key_dim, value_dim = 16, 128, 128
+        slot = heads * key_dim * value_dim
+        wide = 2 * heads * key_dim + 2 * heads * value_dim
+        portions = [PREFILL_TOKENS] if name == "lightning_prefill" else [1] * batch
+        ctx, _ = batch_context(portions, [0 if name == "lightning_prefill" else context] * len(portions))
+        state = torch.zeros(4 * len(portions), slot, device=device)
+        views = [StateView(state, torch.arange(c * len(portions), (c + 1) * len(portions),
+                                               dtype=torch.int32, device=device),
+                           FixedState((slot,), "float32")) for c in range(4)]
+        rows = [torch.randn(ctx.tokens, wide, device=device).bfloat16() for _ in range(4)]
+        constants = dict(decay=torch.full((heads,), 0.97, device=device),
+                         norm_weight=torch.ones(heads * value_dim, device=device), eps=1e-6, ctx=ctx,
+                         write=True, heads=heads, key_dim=key_dim, value_dim=value_dim)
+        run = lambda i: ops.lightning_attention(rows[i % 4], view=views[i % 4], **constants)
+        work = f"{ctx.tokens} tokens of {len(portions)} requests, {heads} heads of {key_dim} x {value_dim}, state {slot * 4 / 1e6:.1f} MB a request"
     else:
         print(f"unknown kernel case {name!r}")
         return 2
@@ -1437,7 +1465,8 @@ def main() -> int:
     parser.add_argument("--kernel", default=None,
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
                              "skinny_in_proj, skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
-                             "swapped_swiglu, mixed_attention, sampling, delta_prefill, delta_decode, decode_step (the "
+                             "swapped_swiglu, mixed_attention, sampling, delta_prefill, delta_decode, lightning_prefill, "
+                             "lightning_decode, decode_step (the "
                              "whole step, eager, for a launch list), decode_timeline (where "
                              "the graph-replayed step's time goes, kernel by kernel)")
     parser.add_argument("--dependent-launches", type=int, default=1,

@@ -5,12 +5,13 @@
 // ([heads][D][V]). The heads' outputs side by side are then divided by their common root mean
 // square, multiplied by a weight and by sigmoid(gate), and stored in the compute dtype.
 //
-// A column of S depends on no other column. The scan gives a column to four lanes of a warp,
-// each of which keeps every fourth group of four rows in registers; a block holds 32 columns of
-// one head of one request and walks the request's tokens of this step in order, eight at a
-// time: the tokens' q and k (silu applied, 32-bit) and the block's slice of v are staged in
-// shared memory, then every thread updates its part of the column and adds its part of o, and
-// two shuffles finish the sum. Everything after the projection's silu is 32-bit.
+// A column of S depends on no other column. A block holds 32 columns of one head of one request:
+// each of its four warps has all 32 columns and every fourth group of four rows of them in
+// registers (a lane = a column, so the state moves 128 bytes at a time). The block walks the
+// request's tokens of this step in order, eight at a time: the tokens' q and k (silu applied,
+// 32-bit) and the block's slice of v are staged in shared memory, then every thread updates its
+// part of the column and adds its share of o, and the four warps' shares meet in shared memory.
+// Everything after the projection's silu is 32-bit.
 //
 // Long portions are cut into segments that run side by side (the recurrence is linear): every
 // segment first builds, from a zero state, what its tokens add to the state; a short pass then
@@ -21,7 +22,7 @@
 namespace {
 
 constexpr int COLS = 32;          // columns of S per block
-constexpr int LANES = 4;          // lanes that share a column
+constexpr int LANES = 4;          // warps that share a column's rows
 constexpr int THREADS = COLS * LANES;
 constexpr int TOK = 8;            // tokens staged at a time
 
@@ -57,15 +58,31 @@ lightning_scan_kernel(ScanArgs a) {
     __shared__ __align__(16) float sq[TOK][DPAD];
     __shared__ __align__(16) float sk[TOK][DPAD];
     __shared__ float sv[TOK][COLS];
+    __shared__ float parts[LANES][TOK][COLS];        // the warps' shares of the outputs
     griddep_launch();
     const int head = blockIdx.y;
     int request = blockIdx.z, piece = 0;
     if (MODE != 0) { request = blockIdx.z / a.max_segments; piece = blockIdx.z % a.max_segments; }
-    const int col = threadIdx.x / LANES, part = threadIdx.x % LANES;
+    // a warp holds 32 neighbouring columns (a row of S is read and written 128 bytes at a time);
+    // the four warps share the rows: warp w keeps the groups of four rows w, w + 4, w + 8, ...
+    const int col = threadIdx.x & 31, part = threadIdx.x >> 5;
     const int j = blockIdx.x * COLS + col;
     const int D = a.key_dim, V = a.value_dim, H = a.heads;
     const bool live = j < V;
     const float decay = a.decay[head];
+    float S[DR];
+    if (MODE == 0) {
+        // the state is what an earlier step left: it is asked for before the kernel ahead of
+        // this one (the projection) is waited for, so that it comes while that one finishes
+        const float* early = a.state + ((size_t)a.slots[request] * H + head) * (size_t)D * V;
+#pragma unroll
+        for (int m = 0; m < DR / 4; ++m)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = 4 * (part + LANES * m) + e;
+                S[4 * m + e] = (live && row < D) ? early[(size_t)row * V + j] : 0.f;
+            }
+    }
     griddep_wait();
     int first = a.request_start[request];
     int last = a.request_start[request + 1];
@@ -86,16 +103,16 @@ lightning_scan_kernel(ScanArgs a) {
     if (MODE != 0)
         carried = a.carried + (((size_t)request * a.max_segments + piece) * H + head) * per_head;
 
-    // this thread's rows: groups of four, group index part + LANES * m
-    float S[DR];
-    const float* from = MODE == 2 && pieces > 1 ? carried : slot;
+    if (MODE != 0) {
+        const float* from = MODE == 2 && pieces > 1 ? carried : slot;
 #pragma unroll
-    for (int m = 0; m < DR / 4; ++m)
+        for (int m = 0; m < DR / 4; ++m)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int row = 4 * (part + LANES * m) + e;
-            S[4 * m + e] = (MODE != 1 && live && row < D) ? from[(size_t)row * V + j] : 0.f;
-        }
+            for (int e = 0; e < 4; ++e) {
+                const int row = 4 * (part + LANES * m) + e;
+                S[4 * m + e] = (MODE != 1 && live && row < D) ? from[(size_t)row * V + j] : 0.f;
+            }
+    }
 
     const T* projected = static_cast<const T*>(a.projected);
     const int q_at = head * D, k_at = H * D + head * D, v_at = 2 * H * D + head * V;
@@ -120,6 +137,8 @@ lightning_scan_kernel(ScanArgs a) {
                 ? silu(to_float<T>(projected[(size_t)(base + t) * a.ld + v_at + column])) : 0.f;
         }
         __syncthreads();
+        // every lane of a warp reads the same k and q (a broadcast); the warp's share of a
+        // token's output waits in shared memory for the other warps'
         for (int t = 0; t < count; ++t) {
             const float v = sv[t][col];
             float sum = 0.f;
@@ -141,10 +160,17 @@ lightning_scan_kernel(ScanArgs a) {
                     }
                 }
             }
-            if (MODE != 1) {
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                if (part == 0 && live) a.o[(size_t)(base + t) * H * V + head * V + j] = sum;
+            if (MODE != 1) parts[part][t][col] = sum;
+        }
+        if (MODE != 1) {
+            __syncthreads();
+            // the four shares of every (token, column) are added in a fixed order
+            for (int item = threadIdx.x; item < count * COLS; item += THREADS) {
+                const int t = item / COLS, c = item % COLS;
+                const int column = blockIdx.x * COLS + c;
+                if (column < V)
+                    a.o[(size_t)(base + t) * H * V + head * V + column] =
+                        (parts[0][t][c] + parts[1][t][c]) + (parts[2][t][c] + parts[3][t][c]);
             }
         }
     }
