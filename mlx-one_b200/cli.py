@@ -10,7 +10,7 @@ from dataclasses import asdict
 import click
 
 
-@click.group(help="B200-native inference engine (LFM2 and Galarax models).")
+@click.group(help="B200-native inference engine (LFM2, Galarax and Farorax models).")
 def main() -> None:
     pass
 
