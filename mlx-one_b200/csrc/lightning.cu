@@ -116,25 +116,73 @@ lightning_scan_kernel(ScanArgs a) {
 
     const T* projected = static_cast<const T*>(a.projected);
     const int q_at = head * D, k_at = H * D + head * D, v_at = 2 * H * D + head * V;
+    // A thread's share of the staging of eight tokens: QN values of q and of k, VN of v. With
+    // AHEAD their raw values for the next eight tokens are loaded into registers before the
+    // current eight are multiplied, and become silu'd 32-bit numbers in shared memory afterwards.
+    constexpr int QN = TOK * DPAD / THREADS, VN = TOK * COLS / THREADS;
+    constexpr bool AHEAD = DR <= 32;
+    float raw_q[AHEAD ? QN : 1], raw_k[AHEAD ? QN : 1], raw_v[AHEAD ? VN : 1];
+    auto fetch = [&](int base, int count) {
+#pragma unroll
+        for (int i = 0; i < QN; ++i) {
+            const int item = threadIdx.x + i * THREADS;
+            const int t = item / DPAD, row = item % DPAD;
+            raw_q[i] = raw_k[i] = 0.f;
+            if (t < count && row < D) {
+                const T* src = projected + (size_t)(base + t) * a.ld;
+                if (MODE != 1) raw_q[i] = to_float<T>(src[q_at + row]);
+                raw_k[i] = to_float<T>(src[k_at + row]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < VN; ++i) {
+            const int item = threadIdx.x + i * THREADS;
+            const int t = item / COLS, column = blockIdx.x * COLS + item % COLS;
+            raw_v[i] = (t < count && column < V)
+                ? to_float<T>(projected[(size_t)(base + t) * a.ld + v_at + column]) : 0.f;
+        }
+    };
+    auto stash = [&](const bool whole, int count) {     // whole: all eight tokens are there
+#pragma unroll
+        for (int i = 0; i < QN; ++i) {
+            const int item = threadIdx.x + i * THREADS;
+            const int t = item / DPAD, row = item % DPAD;
+            if (!whole && t >= count) continue;
+            // (rows beyond the key size hold silu(0) = 0)
+            sq[t][row] = MODE != 1 ? silu(raw_q[i]) : 0.f;
+            sk[t][row] = silu(raw_k[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < VN; ++i) {
+            const int item = threadIdx.x + i * THREADS;
+            if (whole || item / COLS < count) sv[item / COLS][item % COLS] = silu(raw_v[i]);
+        }
+    };
+    if (AHEAD) fetch(first, min(TOK, last - first));
     for (int base = first; base < last; base += TOK) {
         const int count = min(TOK, last - base);
         __syncthreads();
-        for (int item = threadIdx.x; item < count * DPAD; item += THREADS) {
-            const int t = item / DPAD, row = item % DPAD;
-            float q = 0.f, k = 0.f;
-            if (row < D) {
-                const T* src = projected + (size_t)(base + t) * a.ld;
-                if (MODE != 1) q = silu(to_float<T>(src[q_at + row]));
-                k = silu(to_float<T>(src[k_at + row]));
+        if (AHEAD) {
+            if (count == TOK) stash(true, count); else stash(false, count);
+            if (base + TOK < last) fetch(base + TOK, min(TOK, last - base - TOK));
+        } else {
+            for (int item = threadIdx.x; item < count * DPAD; item += THREADS) {
+                const int t = item / DPAD, row = item % DPAD;
+                float q = 0.f, k = 0.f;
+                if (row < D) {
+                    const T* src = projected + (size_t)(base + t) * a.ld;
+                    if (MODE != 1) q = silu(to_float<T>(src[q_at + row]));
+                    k = silu(to_float<T>(src[k_at + row]));
+                }
+                sq[t][row] = q;
+                sk[t][row] = k;
             }
-            sq[t][row] = q;
-            sk[t][row] = k;
-        }
-        for (int item = threadIdx.x; item < count * COLS; item += THREADS) {
-            const int t = item / COLS, c = item % COLS;
-            const int column = blockIdx.x * COLS + c;
-            sv[t][c] = column < V
-                ? silu(to_float<T>(projected[(size_t)(base + t) * a.ld + v_at + column])) : 0.f;
+            for (int item = threadIdx.x; item < count * COLS; item += THREADS) {
+                const int t = item / COLS, c = item % COLS;
+                const int column = blockIdx.x * COLS + c;
+                sv[t][c] = column < V
+                    ? silu(to_float<T>(projected[(size_t)(base + t) * a.ld + v_at + column])) : 0.f;
+            }
         }
         __syncthreads();
         // every lane of a warp reads the same k and q (a broadcast); the warp's share of a

@@ -135,7 +135,8 @@ class RoutedExperts(FeedForward):
         self.router = tensors["router"].to(torch.float32).contiguous()
         # the shared expert once more on its own, for steps that sort their tokens by expert
         self.shared = {}
-        self.sortable = self.activation == "silu" and hasattr(self.ops, "sorts_experts")
+        self.sortable = (self.activation == "silu" and hasattr(self.ops, "sorts_experts")
+                         and runtime.dtype == torch.bfloat16)
         if self.sortable and self.shared_width:
             self.shared = dict(
                 shared_gate_up=self.matrix(torch.cat([tensors["shared.gate"], tensors["shared.up"]], dim=0)),

@@ -151,8 +151,10 @@ class Model:
         self.capturable = all(getattr(part, "capturable", True) for part in parts)
         # For debugging: called as observer(place, residual, delta) after the embedding
         # (place -1) and after every call of a layer (place = its number in the order); the
-        # hidden state there is residual + delta. It sees the step's own tensors: copy what is
-        # to be kept. Steps that are replayed from a CUDA graph do not call it.
+        # hidden state there is residual + s * delta, s the block's ``pending_scale`` (1 unless the
+        # architecture gives its parts' outputs a factor). It sees the step's own tensors (a step's
+        # rows may be followed by fillers): copy what is to be kept. Steps that are replayed from
+        # a CUDA graph do not call it.
         self.observer = None
 
     def forward(self, ctx: StepContext):
@@ -231,6 +233,10 @@ class Model:
         for layer in self.layers:
             visit(layer)
         visit(self.final_norm)
+        for matrix in self.mixing.values():
+            if matrix.data_ptr() not in seen:
+                seen.add(matrix.data_ptr())
+                total += matrix.numel() * matrix.element_size()
         if self.head.data_ptr() not in seen:
             total += self.head.numel() * self.head.element_size()
         return total
