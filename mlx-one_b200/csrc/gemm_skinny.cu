@@ -48,6 +48,8 @@ enum : int { STORE_BF16 = 0, SWIGLU = 1, ADD_RESIDUAL = 2, STORE_F32 = 3, GATED_
              ACTIVATE = 5 };   // ACTIVATE: bf16 store of an activation (its code rides in up_offset)
 // epilogue codes of the C interface from this on mean ACTIVATE with activation (code - this)
 constexpr int ACTIVATE_BASE = 16;
+// ... and from this on the gated epilogue (as SwiGLU) with the gate's activation (code - this)
+constexpr int GATED_BASE = 32;
 constexpr int ONE_BITS = 0x3f800000;      // 1.0f
 
 // What the gated-convolution epilogue needs beside the product: one token per request.
@@ -59,6 +61,8 @@ struct ConvUpdate {
     const int* history = nullptr;      // per request: tokens before this one
     int taps = 1;                      // 1..4
     int write_state = 0;
+    // (rides along for the gated epilogue: the activation of the gate, silu unless said otherwise)
+    int gate = MLXONE_ACT_SILU;
 };
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) {
@@ -610,8 +614,10 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                 }
             } else if (EPILOGUE == SWIGLU) {
                 if (bias != nullptr) up += bias[up_offset + column];
+                const float gate = conv.gate == MLXONE_ACT_SILU ? value / (1.f + expf(-value))
+                                                                : mlxone_activate(value, conv.gate);
                 reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
-                    __float2bfloat16_rn(value / (1.f + expf(-value)) * up);
+                    __float2bfloat16_rn(gate * up);
             } else if (EPILOGUE == STORE_BF16) {
                 reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
                     __float2bfloat16_rn(value);
@@ -749,7 +755,8 @@ MLXONE_API int mlxone_gemm_skinny_scaled_add(const void* a, int lda, const void*
 
 // epilogue: 0 = out bf16 [m, n]; 1 = SwiGLU, w is [gate rows; up rows] with n = 2 * width, out
 // bf16 [m, width]; 2 = out is the float32 residual [m, n], added in place; 3 = out float32;
-// 16 + a = out bf16 [m, n] of activation a (0 relu^2, 1 gelu_tanh, 2 silu, 3 relu).
+// 16 + a = out bf16 [m, n] of activation a (0 relu^2, 1 gelu_tanh, 2 silu, 3 relu); 32 + a = as
+// 1 with the gate's activation a instead of silu.
 MLXONE_API int mlxone_gemm_skinny(const void* a, int lda, const void* w, const float* bias,
                                   void* out, int ldo, int m, int n, int k, int epilogue,
                                   cudaStream_t stream) {
@@ -761,11 +768,18 @@ MLXONE_API int mlxone_gemm_skinny(const void* a, int lda, const void* w, const f
                        (reinterpret_cast<uintptr_t>(w) & 15) == 0,
                    "gemm_skinny: operands must be 16-byte aligned");
     MLXONE_REQUIRE((epilogue >= 0 && epilogue <= 3) ||
-                       (epilogue >= ACTIVATE_BASE && epilogue <= ACTIVATE_BASE + MLXONE_ACT_RELU),
+                       (epilogue >= ACTIVATE_BASE && epilogue <= ACTIVATE_BASE + MLXONE_ACT_RELU) ||
+                       (epilogue >= GATED_BASE && epilogue <= GATED_BASE + MLXONE_ACT_RELU),
                    "gemm_skinny: unknown epilogue %d", epilogue);
-    MLXONE_REQUIRE(epilogue != SWIGLU || n % 2 == 0, "gemm_skinny: SwiGLU needs an even n");
+    MLXONE_REQUIRE((epilogue != SWIGLU && epilogue < GATED_BASE) || n % 2 == 0,
+                   "gemm_skinny: a gated epilogue needs an even n");
     cudaError_t err;
-    if (epilogue >= ACTIVATE_BASE) {
+    if (epilogue >= GATED_BASE) {
+        ConvUpdate gated;
+        gated.gate = epilogue - GATED_BASE;
+        err = launch_for_rows<SWIGLU>(a, lda, w, bias, out, ldo, m, n, k, n / 2, stream, NormInput(),
+                                      gated);
+    } else if (epilogue >= ACTIVATE_BASE) {
         err = launch_for_rows<ACTIVATE>(a, lda, w, bias, out, ldo, m, n, k, epilogue - ACTIVATE_BASE,
                                         stream);
     } else
@@ -883,13 +897,20 @@ MLXONE_API int mlxone_gemm_skinny_norm(const float* source, int source_ld,
                        (reinterpret_cast<uintptr_t>(w) & 15) == 0,
                    "gemm_skinny_norm: operands must be 16-byte aligned");
     MLXONE_REQUIRE((epilogue >= 0 && epilogue <= 3) ||
-                       (epilogue >= ACTIVATE_BASE && epilogue <= ACTIVATE_BASE + MLXONE_ACT_RELU),
+                       (epilogue >= ACTIVATE_BASE && epilogue <= ACTIVATE_BASE + MLXONE_ACT_RELU) ||
+                       (epilogue >= GATED_BASE && epilogue <= GATED_BASE + MLXONE_ACT_RELU),
                    "gemm_skinny_norm: unknown epilogue %d", epilogue);
-    MLXONE_REQUIRE(epilogue != SWIGLU || n % 2 == 0, "gemm_skinny_norm: SwiGLU needs an even n");
+    MLXONE_REQUIRE((epilogue != SWIGLU && epilogue < GATED_BASE) || n % 2 == 0,
+                   "gemm_skinny_norm: a gated epilogue needs an even n");
     NormInput norm;
     norm.source = source; norm.ld = source_ld; norm.weight = norm_weight; norm.eps = eps;
     cudaError_t err;
-    if (epilogue >= ACTIVATE_BASE) {
+    if (epilogue >= GATED_BASE) {
+        ConvUpdate gated;
+        gated.gate = epilogue - GATED_BASE;
+        err = launch_for_rows<SWIGLU>(nullptr, 0, w, bias, out, ldo, m, n, k, n / 2, stream, norm,
+                                      gated);
+    } else if (epilogue >= ACTIVATE_BASE) {
         err = launch_for_rows<ACTIVATE>(nullptr, 0, w, bias, out, ldo, m, n, k,
                                         epilogue - ACTIVATE_BASE, stream, norm);
     } else

@@ -216,6 +216,7 @@ class CudaOps:
     # epilogues of the skinny product
     _STORE, _SWIGLU, _ADD, _STORE_F32 = 0, 1, 2, 3
     _ACTIVATE = 16          # + the activation's code: a bfloat16 store of the activated product
+    _GATED = 32             # + the activation's code: as _SWIGLU with that gate
 
     def _skinny(self, a, w, fused=False) -> bool:
         """Whether a[M, K] @ w[N, K]^T goes to the weight-streaming kernel: bfloat16, few rows,
@@ -408,13 +409,24 @@ class CudaOps:
 
     def linear_gated(self, a, gate_up, kind):
         """act(a @ gate^T) * (a @ up^T) with gate_up = [gate rows; up rows], for the activations
-        of ``ACTIVATIONS``: silu takes the fused kernels of ``linear_swiglu``; the others run the
-        product (with the norm of its input applied while loading, for few rows) and one kernel
-        for the gate."""
+        of ``ACTIVATIONS``: silu takes the fused kernels of ``linear_swiglu``; for the others the
+        gate is the skinny product's epilogue for few rows (also with the norm of its input
+        applied while loading), else the product and one kernel for the gate."""
         if kind == "silu":
             return self.linear_swiglu(a, gate_up)
         if kind not in self.ACTIVATIONS:
             raise KernelError(f"unknown activation {kind!r}")
+        epilogue = self._GATED + self.ACTIVATIONS[kind]
+        width = gate_up.shape[0] // 2
+        if isinstance(a, NormedInput):
+            out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
+            self._normed_call(a, gate_up, None, out, width, epilogue)
+            return out
+        self._check_product(a, gate_up)
+        if self._skinny(a, gate_up, fused=True):
+            out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
+            self._skinny_call(a, gate_up, None, out, width, epilogue)
+            return out
         both = self.linear(a, gate_up)
         rows, twice = both.shape
         out = torch.empty((rows, twice // 2), dtype=both.dtype, device=self.device)
