@@ -546,14 +546,17 @@ class CudaOps:
                    _c_int(width), _c_int(_dtype_code(gated.dtype)))
 
     # Steps of at least this many tokens run routed experts over tokens sorted by expert (grouped
-    # tcgen05 products that touch only the experts a token uses); smaller steps run every token
-    # through all experts in one stacked product, which reads the same weights at those sizes.
+    # tcgen05 products that touch only the experts a token uses), and so do steps so small that
+    # their tokens use at most half of the experts (a single token that uses 2 of 8, or 6 of 64,
+    # should not read them all); the steps between run every token through all experts in one
+    # stacked product, which reads the same weights at those sizes with fewer launches.
     sorted_experts_min_tokens = 128
 
     def sorts_experts(self, x, *, experts, width, top, stack) -> bool:
         """Whether ``routed_experts_sorted`` takes this step."""
+        tokens = x.shape[0]
         return (self.tcgen05_products and x.dtype == torch.bfloat16 and top < experts
-                and x.shape[0] >= self.sorted_experts_min_tokens
+                and (tokens >= self.sorted_experts_min_tokens or 2 * tokens * top <= experts)
                 and x.shape[1] % 8 == 0 and width % 8 == 0 and stack % 8 == 0
                 and x.stride(1) == 1 and x.stride(0) % 8 == 0)
 
@@ -572,8 +575,9 @@ class CudaOps:
         self._call("mlxone_sort_by_expert", _c_void_p(_ptr(weights)), _c_void_p(_ptr(pair_row)),
                    _c_void_p(_ptr(groups)), _c_int(tokens), _c_int(experts), _c_int(width),
                    _c_int(tiles))
-        # (rows that no pair owns are never read back; zeros keep their products finite)
-        sorted_x = torch.zeros((rows, hidden), dtype=x.dtype, device=self.device)
+        # (rows that no pair owns are multiplied like the others, but nothing reads their results,
+        # and a row's result depends on no other row: they need no values of their own)
+        sorted_x = torch.empty((rows, hidden), dtype=x.dtype, device=self.device)
         self._call("mlxone_gather_by_expert", _c_void_p(_ptr(x)), _c_int(x.stride(0)),
                    _c_void_p(_ptr(pair_row)), _c_void_p(_ptr(sorted_x)), _c_int(tokens),
                    _c_int(hidden), _c_int(experts), _c_int(_dtype_code(x.dtype)))

@@ -318,11 +318,11 @@ def test_experts_as_columns_of_one_product(ops, dtype):
 
 @pytest.mark.parametrize("tokens, hidden, experts, width, top, shared", [
     (300, 128, 6, 72, 2, 40), (1000, 256, 8, 256, 3, None), (129, 64, 16, 8, 1, 8),
-    (2048, 192, 4, 136, 3, 136)])
+    (2048, 192, 4, 136, 3, 136), (1, 128, 8, 64, 2, 64), (3, 256, 64, 32, 6, None)])
 def test_experts_over_sorted_tokens(ops, tokens, hidden, experts, width, top, shared):
-    """Large steps in bfloat16: tokens sorted by expert and one grouped product per matrix over
-    the stacked weights, against every expert applied to its tokens one by one. Some experts get
-    no token at all, others more than a tile."""
+    """Large steps in bfloat16, and steps so small that they use few of the experts: tokens sorted
+    by expert and one grouped product per matrix over the stacked weights, against every expert
+    applied to its tokens one by one. Some experts get no token at all, others more than a tile."""
     generator = torch.Generator().manual_seed(tokens + experts)
     x = torch.randn(tokens, hidden, generator=generator).bfloat16()
     stack = experts * width + (shared or 0)
