@@ -907,7 +907,7 @@ def farorax_shape(width: int, layers: int, vocab: int = 65536) -> dict:
         mixer = ("attention", attention) if index % 4 == 0 else ("lightning", lightning)
         entries.append({"type": mixer[0], "mixer": mixer[1], "mlp": routed if index % 2 else dense})
     return {"architecture": "Farorax", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "residual_mult": 0.3, "logit_softcap": 30.0, "layers": entries}
+            "residual_mult": 0.5, "logit_softcap": 50.0, "layers": entries}
 
 
 def farorax_kernels(width, batch, peak):
@@ -1051,14 +1051,14 @@ def farorax_kernels(width, batch, peak):
         vector = torch.zeros(width, device=device)
 
         def enter(i):
-            both = ops.concat_stream(residual[i], delta[i], ids, table_e, torch.bfloat16, delta_scale=0.3)
+            both = ops.concat_stream(residual[i], delta[i], ids, table_e, torch.bfloat16, delta_scale=0.5)
             return ops.linear(both, mix, vector, out_dtype=torch.float32)
         seconds = graph_seconds(enter, 4, 8)
         out[f"{label}_loop_entry_mix"] = entry(seconds, tokens * width * (4 + 2 + 2 + 4 + 4) + mix.numel() * 2)
         seconds = graph_seconds(lambda i: ops.add_vectors(residual[i], delta[i], ids, table_e, vector), 4, 8)
         out[f"{label}_loop_entry_add_galarax"] = entry(seconds, tokens * width * (4 + 2 + 2 + 4))
         seconds = graph_seconds(lambda i: ops.add_rmsnorm(residual[i], delta[i], vector, 1e-6,
-                                                          torch.bfloat16, delta_scale=0.3), 4, 8)
+                                                          torch.bfloat16, delta_scale=0.5), 4, 8)
         out[f"{label}_add_rmsnorm_scaled"] = entry(seconds, tokens * width * (4 + 4 + 2 + 2))
         del residual, delta
         torch.cuda.empty_cache()

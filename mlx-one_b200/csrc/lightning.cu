@@ -59,6 +59,12 @@ lightning_scan_kernel(ScanArgs a) {
     __shared__ __align__(16) float sk[TOK][DPAD];
     __shared__ float sv[TOK][COLS];
     __shared__ float parts[LANES][TOK][COLS];        // the warps' shares of the outputs
+    // Within a group of eight tokens the state is kept divided by the decay's powers, so that
+    // the recurrence costs one multiply-add per element and token instead of a multiply and a
+    // multiply-add: token i's k is staged times decay^-(i+1), its q times decay^(i+1), and the
+    // state is multiplied by decay^count after the group. Not for decays below 0.01, whose
+    // inverse powers would leave the range of 32-bit numbers (they keep the plain form).
+    __shared__ float kfac[TOK], qfac[TOK];
     griddep_launch();
     const int head = blockIdx.y;
     int request = blockIdx.z, piece = 0;
@@ -70,6 +76,13 @@ lightning_scan_kernel(ScanArgs a) {
     const int D = a.key_dim, V = a.value_dim, H = a.heads;
     const bool live = j < V;
     const float decay = a.decay[head];
+    const bool scaled = decay >= 0.01f;
+    if (threadIdx.x < TOK) {
+        double power = 1.0;
+        for (int i = 0; i <= (int)threadIdx.x; ++i) power *= (double)decay;
+        qfac[threadIdx.x] = scaled ? (float)power : 1.f;
+        kfac[threadIdx.x] = scaled ? (float)(1.0 / power) : 1.f;
+    }
     float S[DR];
     if (MODE == 0) {
         // the state is what an earlier step left: it is asked for before the kernel ahead of
@@ -149,8 +162,8 @@ lightning_scan_kernel(ScanArgs a) {
             const int t = item / DPAD, row = item % DPAD;
             if (!whole && t >= count) continue;
             // (rows beyond the key size hold silu(0) = 0)
-            sq[t][row] = MODE != 1 ? silu(raw_q[i]) : 0.f;
-            sk[t][row] = silu(raw_k[i]);
+            sq[t][row] = MODE != 1 ? silu(raw_q[i]) * qfac[t] : 0.f;
+            sk[t][row] = silu(raw_k[i]) * kfac[t];
         }
 #pragma unroll
         for (int i = 0; i < VN; ++i) {
@@ -171,8 +184,8 @@ lightning_scan_kernel(ScanArgs a) {
                 float q = 0.f, k = 0.f;
                 if (row < D) {
                     const T* src = projected + (size_t)(base + t) * a.ld;
-                    if (MODE != 1) q = silu(to_float<T>(src[q_at + row]));
-                    k = silu(to_float<T>(src[k_at + row]));
+                    if (MODE != 1) q = silu(to_float<T>(src[q_at + row])) * qfac[t];
+                    k = silu(to_float<T>(src[k_at + row])) * kfac[t];
                 }
                 sq[t][row] = q;
                 sk[t][row] = k;
@@ -187,28 +200,60 @@ lightning_scan_kernel(ScanArgs a) {
         __syncthreads();
         // every lane of a warp reads the same k and q (a broadcast); the warp's share of a
         // token's output waits in shared memory for the other warps'
-        for (int t = 0; t < count; ++t) {
-            const float v = sv[t][col];
-            float sum = 0.f;
+        if (scaled) {
+            // S is kept divided by decay^(tokens of this group so far), k and q were staged times
+            // decay^-(i+1) and decay^(i+1): an update and a sum are one multiply-add each
+            for (int t = 0; t < count; ++t) {
+                const float v = sv[t][col];
+                float sum[4] = {0.f, 0.f, 0.f, 0.f};      // four chains of additions, not one
 #pragma unroll
-            for (int m = 0; m < DR / 4; ++m) {
-                const int at = 4 * (part + LANES * m);
-                const float4 k4 = *reinterpret_cast<const float4*>(&sk[t][at]);
-                const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
-                if (MODE == 1) {
+                for (int m = 0; m < DR / 4; ++m) {
+                    const int at = 4 * (part + LANES * m);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&sk[t][at]);
+                    const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+                    if (MODE == 1) {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) S[4 * m + e] = fmaf(decay, S[4 * m + e], kk[e] * v);
-                } else {
-                    const float4 q4 = *reinterpret_cast<const float4*>(&sq[t][at]);
-                    const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+                        for (int e = 0; e < 4; ++e) S[4 * m + e] = fmaf(kk[e], v, S[4 * m + e]);
+                    } else {
+                        const float4 q4 = *reinterpret_cast<const float4*>(&sq[t][at]);
+                        const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        S[4 * m + e] = fmaf(decay, S[4 * m + e], kk[e] * v);
-                        sum = fmaf(S[4 * m + e], qq[e], sum);
+                        for (int e = 0; e < 4; ++e) {
+                            S[4 * m + e] = fmaf(kk[e], v, S[4 * m + e]);
+                            sum[e] = fmaf(S[4 * m + e], qq[e], sum[e]);
+                        }
                     }
                 }
+                if (MODE != 1) parts[part][t][col] = (sum[0] + sum[1]) + (sum[2] + sum[3]);
             }
-            if (MODE != 1) parts[part][t][col] = sum;
+            const float back = qfac[count - 1];            // decay^count
+#pragma unroll
+            for (int i = 0; i < DR; ++i) S[i] *= back;
+        } else {
+            for (int t = 0; t < count; ++t) {
+                const float v = sv[t][col];
+                float sum = 0.f;
+#pragma unroll
+                for (int m = 0; m < DR / 4; ++m) {
+                    const int at = 4 * (part + LANES * m);
+                    const float4 k4 = *reinterpret_cast<const float4*>(&sk[t][at]);
+                    const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+                    if (MODE == 1) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            S[4 * m + e] = fmaf(decay, S[4 * m + e], kk[e] * v);
+                    } else {
+                        const float4 q4 = *reinterpret_cast<const float4*>(&sq[t][at]);
+                        const float qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            S[4 * m + e] = fmaf(decay, S[4 * m + e], kk[e] * v);
+                            sum = fmaf(S[4 * m + e], qq[e], sum);
+                        }
+                    }
+                }
+                if (MODE != 1) parts[part][t][col] = sum;
+            }
         }
         if (MODE != 1) {
             __syncthreads();

@@ -80,8 +80,8 @@ F3 = {"architecture": "Farorax", "vocab": 512, "width": 128, "norm": {"eps": 2e-
       "residual_mult": 0.7, "logit_softcap": 15.0,
       "layers": [
           lightning(4, 128, 32, (0.95, 0.9, 0.99, 0.7), dense(256)),
-          attention(8, 1, 64, 64, 0.11, 100, _LONG_B, routed(64, 8, 3, (4, 2), 64)),
-          lightning(4, 128, 32, (0.95, 0.9, 0.99, 0.7), routed(64, 8, 3, (4, 2), 64)),
+          attention(8, 1, 64, 64, 0.11, 100, _LONG_B, routed(48, 8, 3, (4, 2), 64)),
+          lightning(4, 128, 32, (0.95, 0.9, 0.99, 0.7), routed(48, 8, 3, (4, 2), 64)),
           attention(8, 1, 64, 64, 0.11, 100, _LONG_B, dense(256))],
       "loop": {"start": 1, "stop": 2, "times": 3}}
 

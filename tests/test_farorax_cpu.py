@@ -113,7 +113,7 @@ def test_order_of_calls_and_weight_contract():
     names = expected_tensors(spec)
     assert names["loop.in"].shape == (128, 256) and names["loop.step"].shape == (3, 128)
     assert names["l1.mix.sink"].shape == (8,) and names["l1.mix.o"].shape == (128, 8 * 64)
-    assert names["l2.mlp.router"].shape == (8, 128) and names["l2.mlp.e7.down"].shape == (128, 64)
+    assert names["l2.mlp.router"].shape == (8, 128) and names["l2.mlp.e7.down"].shape == (128, 48)
     assert names["l2.mlp.shared.gate"].shape == (64, 128) and names["l0.mix.norm"].shape == (128,)
     assert "l0.mix.sink" not in names and "l3.mlp.router" not in names
     five = expected_tensors(describe(FaroraxConfig.from_dict(F5)))
