@@ -1338,6 +1338,28 @@ def kernel_case(name: str, batch: int, context: int) -> int:
                          ctx=ctx, write=True, **sizes)
         run = lambda i: ops.gated_delta_rule(rows[i % 4], view=views[i % 4], **constants)
         work = f"{ctx.tokens} tokens of {len(portions)} requests, 16 heads of 128 x 128, state {slot * 4 / 1e6:.1f} MB a request"
+    elif name == "experts_sorted":
+        # a routed feed-forward over 2,048 tokens sorted by expert: 8 experts of the model's width,
+        # 2 a token, beside a shared one (sort, gather, two grouped tcgen05 products, the shared
+        # expert's two products, combine)
+        experts, top, ff, shared = 8, 2, hidden, hidden
+        stack = experts * ff + shared
+        gate_up = weights(2 * stack, hidden, 2)
+        down = weights(hidden, stack, 2)
+        at = experts * ff
+        alone = [(torch.cat([g[at:at + shared], g[stack + at:stack + at + shared]]).contiguous(),
+                  d[:, at:].contiguous()) for g, d in zip(gate_up, down)]
+        router = torch.randn(experts, hidden, device=device)
+        x = torch.randn(PREFILL_TOKENS, hidden, device=device).bfloat16()
+
+        def run(i):
+            routing = ops.route_experts(x, router, experts=experts, top=top, groups=4, keep=2,
+                                        group_score=2)
+            return ops.routed_experts_sorted(x, routing, gate_up[i % 2], down[i % 2], experts=experts,
+                                             width=ff, top=top, shared_gate_up=alone[i % 2][0],
+                                             shared_down=alone[i % 2][1])
+        work = (f"{PREFILL_TOKENS} tokens, {experts} experts of {ff} x {hidden}, {top} a token, shared {shared}: "
+                f"{6.0 * PREFILL_TOKENS * (top * ff + shared) * hidden / 1e9:.0f} GFLOP")
     elif name in ("lightning_prefill", "lightning_decode"):
         # lightning attention at the shape of a 2048-wide model: one 2,048-token prompt (segments:
         # build, chain, scan, then the norm and gate) or `batch` single tokens (scan, norm and gate)
@@ -1466,7 +1488,7 @@ def main() -> int:
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
                              "skinny_in_proj, skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
                              "swapped_swiglu, mixed_attention, sampling, delta_prefill, delta_decode, lightning_prefill, "
-                             "lightning_decode, decode_step (the "
+                             "lightning_decode, experts_sorted, decode_step (the "
                              "whole step, eager, for a launch list), decode_timeline (where "
                              "the graph-replayed step's time goes, kernel by kernel)")
     parser.add_argument("--dependent-launches", type=int, default=1,

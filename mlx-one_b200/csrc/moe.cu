@@ -150,37 +150,91 @@ sort_by_expert_kernel(const float* __restrict__ weights, int* __restrict__ pair_
         if (pair_row[i] >= 0) pair_row[i] += start[i % experts];
 }
 
-// sorted[pair_row[t, e], :] = x[t, :] for every chosen pair. One block per token.
+// sorted[pair_row[t, e], :] = x[t, :] for every chosen pair. One block per token; 16 bytes a
+// copy where the rows allow it.
 template <typename T>
 __global__ void gather_by_expert_kernel(const T* __restrict__ x, int ld, const int* __restrict__ pair_row,
                                         T* __restrict__ sorted, int hidden, int experts) {
     griddep_launch();
     griddep_wait();
     const int t = blockIdx.x;
+    constexpr int PER = 16 / sizeof(T);
+    const bool wide = hidden % PER == 0 && ld % PER == 0 &&
+                      (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                      (reinterpret_cast<uintptr_t>(sorted) & 15) == 0;
     for (int e = 0; e < experts; ++e) {
         const int row = pair_row[(size_t)t * experts + e];
         if (row < 0) continue;
-        for (int c = threadIdx.x; c < hidden; c += blockDim.x)
-            sorted[(size_t)row * hidden + c] = x[(size_t)t * ld + c];
+        const T* from = x + (size_t)t * ld;
+        T* to = sorted + (size_t)row * hidden;
+        if (wide) {
+            for (int c = threadIdx.x * PER; c < hidden; c += blockDim.x * PER)
+                *reinterpret_cast<uint4*>(to + c) = *reinterpret_cast<const uint4*>(from + c);
+        } else {
+            for (int c = threadIdx.x; c < hidden; c += blockDim.x) to[c] = from[c];
+        }
     }
 }
 
 // out[t, :] = sum over chosen e of weights[t, e] * y[pair_row[t, e], :] (+ shared[t, :]), in
-// 32-bit, experts in ascending order.
+// 32-bit, experts in ascending order. The token's pairs are looked up once, by one thread.
+constexpr int MAX_TOP = 64;
+
 template <typename T>
 __global__ void combine_experts_kernel(const T* __restrict__ y, const int* __restrict__ pair_row,
                                        const float* __restrict__ weights, const T* __restrict__ shared_out,
                                        T* __restrict__ out, int hidden, int experts) {
+    __shared__ int rows[MAX_TOP];
+    __shared__ float factors[MAX_TOP];
+    __shared__ int chosen;
     griddep_launch();
     griddep_wait();
     const int t = blockIdx.x;
+    if (threadIdx.x == 0) {
+        int count = 0;
+        for (int e = 0; e < experts && count < MAX_TOP; ++e) {
+            const int row = pair_row[(size_t)t * experts + e];
+            if (row >= 0) {
+                rows[count] = row;
+                factors[count++] = weights[(size_t)t * experts + e];
+            }
+        }
+        chosen = count;
+    }
+    __syncthreads();
+    const int count = chosen;
+    constexpr int PER = 8 / sizeof(T);            // 4 bfloat16 or 2 floats a load
+    const bool wide = hidden % PER == 0 && (reinterpret_cast<uintptr_t>(y) & 7) == 0 &&
+                      (reinterpret_cast<uintptr_t>(out) & 7) == 0 &&
+                      (reinterpret_cast<uintptr_t>(shared_out) & 7) == 0;
+    if (wide) {
+        for (int c = threadIdx.x * PER; c < hidden; c += blockDim.x * PER) {
+            float sum[PER];
+            __align__(8) T piece[PER];
+#pragma unroll
+            for (int i = 0; i < PER; ++i) sum[i] = 0.f;
+            if (shared_out != nullptr) {
+                *reinterpret_cast<uint2*>(piece) =
+                    *reinterpret_cast<const uint2*>(shared_out + (size_t)t * hidden + c);
+#pragma unroll
+                for (int i = 0; i < PER; ++i) sum[i] = to_float<T>(piece[i]);
+            }
+            for (int k = 0; k < count; ++k) {
+                *reinterpret_cast<uint2*>(piece) =
+                    *reinterpret_cast<const uint2*>(y + (size_t)rows[k] * hidden + c);
+#pragma unroll
+                for (int i = 0; i < PER; ++i) sum[i] = fmaf(factors[k], to_float<T>(piece[i]), sum[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < PER; ++i) piece[i] = from_float<T>(sum[i]);
+            *reinterpret_cast<uint2*>(out + (size_t)t * hidden + c) = *reinterpret_cast<uint2*>(piece);
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
         float sum = shared_out != nullptr ? to_float<T>(shared_out[(size_t)t * hidden + c]) : 0.f;
-        for (int e = 0; e < experts; ++e) {
-            const int row = pair_row[(size_t)t * experts + e];
-            if (row >= 0)
-                sum = fmaf(weights[(size_t)t * experts + e], to_float<T>(y[(size_t)row * hidden + c]), sum);
-        }
+        for (int k = 0; k < count; ++k)
+            sum = fmaf(factors[k], to_float<T>(y[(size_t)rows[k] * hidden + c]), sum);
         out[(size_t)t * hidden + c] = from_float<T>(sum);
     }
 }

@@ -5,7 +5,7 @@ The configurations differ in every size: width, vocabulary, head counts and grou
 value sizes (equal, value shorter, value longer; multiples of 32, of 16, of neither), the
 rotated part of a head (all of it, a part, two dimensions, nothing) with and without the
 long-context rule, windows (shorter than a page, a few pages, longer than every prompt, none,
-one token), lightning heads with keys of 16 to 136 values and decays from fast to almost none,
+one token), lightning heads with keys of 4 to 136 values and decays from fast to none at all,
 feed-forwards (gated, routed with and without groups and a shared expert, one expert per token,
 none), the order of the layers, the factor on the parts' outputs (also 1), the soft cap (also
 none), and the loop (over the first layers, a single layer three times, all layers once, the
