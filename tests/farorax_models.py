@@ -171,16 +171,16 @@ USUAL_NOISE = 5e-6
 # The bfloat16 engine routes what its own 16-bit arithmetic has made of the stream (about a
 # percent from the plain model's), so a position whose routing margin is below this may go to
 # other experts than in the plain model; its own logits are then others, and so, a little, are
-# those of every later position of the request (the layers after it carry it on). Rows from the
-# first such position on are held to the looser rule below.
+# those of every later position of the request (the layers after it carry it on: a lightning
+# state forgets slowly). Rows from the first such position on are not compared in bfloat16; the
+# 32-bit engine is compared everywhere, and so is bfloat16 on models without routed experts.
 ROUTING_MARGIN = 0.05
 
 
 def assert_rows_close(got: torch.Tensor, want: torch.Tensor, dtype, what: str = "") -> None:
     """float32: every logit within 1e-4 + 1e-4 |plain| + 4 x the position's noise (positions with
     a routing margin below 1e-5 left out). bfloat16: every row's error (see above) within
-    ``BF16_ROW_ERROR`` up to the first position that is routed by a hair; of the rows from there
-    on, two in three."""
+    ``BF16_ROW_ERROR`` up to the request's first position that is routed by a hair."""
     noise, margin = getattr(want, "noise", None), getattr(want, "margin", None)
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, f"{what}: {tuple(got.shape)} against {tuple(want.shape)}"
@@ -201,9 +201,6 @@ def assert_rows_close(got: torch.Tensor, want: torch.Tensor, dtype, what: str = 
     bad = (rows > allowed) & settled
     assert not bad.any(), (f"{what}: row error {rows[settled].max():.3f} of the spread; rows "
                            f"{torch.nonzero(bad).flatten().tolist()[:8]}")
-    if (~settled).any():
-        within = (rows[~settled] <= allowed[~settled]).float().mean()
-        assert within >= 0.66, f"{what}: only {within:.2f} of the rows behind a close routing agree"
 
 
 def sliced(want: torch.Tensor, count: int) -> torch.Tensor:

@@ -1,6 +1,6 @@
 """Farorax models whose every size and constant is drawn at random (seeded): the 32-bit engine
 against the plain model over whole requests, decoded tails, portions and mixed batches; the
-bfloat16 engine over the same, held to the looser rule for rows behind a close routing."""
+bfloat16 engine over the same, up to each request's first position that is routed by a hair."""
 
 import random
 
